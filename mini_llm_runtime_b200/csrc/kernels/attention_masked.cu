@@ -7,12 +7,16 @@
 //   rotation:   the first rot_dims values of each head of q and k turned by p * freq[i], value i paired
 //               with value i + rot_dims / 2; the rest pass.  Angles, cosines and sines are float32 and
 //               computed from the position (no table, no largest position).
-//   sink:       softmax with exp(0) added to the denominator (a key of score 0 without a value)
-//   gate:       out *= sigmoid(gate) or silu(gate), element by element, and a constant factor
+//   kept first tokens:   with a window, keys j < keep_first stay visible however far back they lie
+//   score:      (q . k) * scale;  with softcap > 0 then softcap * tanh(score / softcap);  with slopes then minus
+//               slopes[head] * (p - j), a bias that grows with the distance
+//   sink:       softmax with exp(sink_h) added to the denominator (a key without a value whose score is a learned number
+//               per head, or 0 where none is given)
+//   gate:       out *= sigmoid(gate) or silu(gate), element by element (or sigmoid of ONE value per head), and a constant factor
 //
 // Cache of a layer: per page, the keys [kv_head][token_in_page][dim] and then the values
-// [kv_head][token_in_page][vdim] (with shared_kv only the keys, which are the values too).  `mlr_kv_rope_cache` rotates the step's keys and writes keys and
-// values; `mlr_attention_masked` rotates its query as it loads it and walks the visible keys in tiles
+// [kv_head][token_in_page][vdim] (with shared_kv only the keys: a token's value is the first vdim values of its key).  `mlr_kv_rope_cache` rotates the step's keys and writes keys and
+// values (`mlr_qkv_prepare_cache` first adds biases, divides heads by their root mean square and mixes in the values an earlier layer made of the same tokens); `mlr_attention_masked` rotates its query as it loads it and walks the visible keys in tiles
 // of 64 with a running maximum, one block per (row, query head), so a row's result depends on its
 // position and on the cache only.  Scores, weights and sums are float32; q, the cache, the gate and
 // the output are float32 or bfloat16.  Keys that are not visible are never loaded.  That kernel serves
@@ -22,12 +26,28 @@
 
 struct MaskedAttentionSpec {
     const float* freq;     // [rot_dims / 2] float32 on the device, or null
+    const float* sinks;    // [heads] float32 on the device: the sink's score per head; null with sink set: 0
+    const float* slopes;   // [heads] float32 on the device: score -= slopes[head] * distance; null: no such bias
     int heads, kv_heads, dim, vdim;
     int rot_dims, window, chunk, sink;
-    int gate_kind;         // 0 none, 1 sigmoid, 2 silu
-    int shared_kv;         // 1: a token's value IS its key (vdim == dim; one vector per token is cached and a page holds keys only)
+    int gate_kind;         // 0 none, 1 sigmoid, 2 silu, 3 sigmoid of one value per head (the gate has `heads` columns)
+    int shared_kv;         // 1: a token's value is the first vdim values of its key (vdim <= dim; one vector per token is cached and a page holds keys only)
+    int keep_first;        // with a window: the first keep_first positions stay visible
     float scale, out_scale;
+    float softcap;         // > 0: score <- softcap * tanh(score / softcap)
 };
+
+// What a score becomes after the product: scaled, capped, biased by the distance to the key.
+__device__ __forceinline__ float mlr_masked_score(float dot, int distance, float slope, const MaskedAttentionSpec& s) {
+    float score = dot * s.scale;
+    if (s.softcap > 0.0f) score = s.softcap * tanhf(score / s.softcap);
+    return score - slope * static_cast<float>(distance);
+}
+
+__device__ __forceinline__ float mlr_gate_value(float g, int kind) {
+    const float sig = 1.0f / (1.0f + expf(-g));
+    return kind == 2 ? g * sig : sig;
+}
 
 namespace {
 
@@ -75,6 +95,81 @@ __global__ void __launch_bounds__(kThreads) kv_rope_cache_kernel(const T* k, int
     mlr_grid_dependents_may_start();
 }
 
+// The step's q, k and v as the projection left them, made ready for attention, one block per row and one warp per head:
+//   q_h <- (q_h + bias) / rms(q_h)          in place         (biases and the division only where asked for)
+//   k_g <- (k_g + bias) / rms(k_g), rotated like `kv_rope_cache_kernel` does, into the cache
+//   v_g <- (v_g + bias) / rms(v_g);  mix 1: first[row] = v;  mix 2: v <- (1 - lambda) v + lambda first[row];  into the cache
+// `first` is a float32 buffer of the step, [rows, kv_heads * vdim]: the values the first of several layers made of the same
+// tokens, which the later ones mix into their own.  All arithmetic is float32.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int ldq, const T* k, int ld_k, const T* v, int ld_v, const float* bq,
+                                                                     const float* bk, const float* bv, int unit_qk, int unit_v, float eps,
+                                                                     float* first, int ld_first, int mix, float lambda, T* cache, int num_pages,
+                                                                     const int* positions, const int* segment_of_row, const int* block_table,
+                                                                     int table_stride, int page_size, MaskedAttentionSpec s, int* status) {
+    mlr_grid_wait();
+    extern __shared__ __align__(16) float staged[];        // [warps][max(dim, vdim)]
+    const int row = blockIdx.x;
+    const int position = positions[row];
+    const int page = block_table[static_cast<size_t>(segment_of_row[row]) * table_stride + position / page_size];
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
+        return;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* mine = staged + warp * max(s.dim, s.vdim);
+    const size_t page_elems = static_cast<size_t>(s.kv_heads) * page_size * (s.dim + s.vdim);
+    T* kbase = cache + page * page_elems + static_cast<size_t>(position % page_size) * s.dim;
+    T* vbase = cache + page * page_elems + static_cast<size_t>(s.kv_heads) * page_size * s.dim +
+               static_cast<size_t>(position % page_size) * s.vdim;
+    const int half = s.rot_dims / 2;
+    const float p = static_cast<float>(position);
+    for (int unit = warp; unit < s.heads + 2 * s.kv_heads; unit += kThreads / 32) {
+        const int kind = unit < s.heads ? 0 : (unit < s.heads + s.kv_heads ? 1 : 2);
+        const int head = kind == 0 ? unit : (kind == 1 ? unit - s.heads : unit - s.heads - s.kv_heads);
+        const int n = kind == 2 ? s.vdim : s.dim;
+        const T* src = kind == 0 ? q + static_cast<size_t>(row) * ldq : (kind == 1 ? k + static_cast<size_t>(row) * ld_k : v + static_cast<size_t>(row) * ld_v);
+        const float* bias = kind == 0 ? bq : (kind == 1 ? bk : bv);
+        float squares = 0.0f;
+        for (int c = lane; c < n; c += 32) {
+            float value = mlr_load(src, static_cast<size_t>(head) * n + c);
+            if (bias) value += bias[head * n + c];
+            mine[c] = value;
+            squares = fmaf(value, value, squares);
+        }
+        const bool unit_norm = kind == 2 ? unit_v : unit_qk;
+        const float inv = unit_norm ? 1.0f / sqrtf(mlr_warp_sum(squares) / static_cast<float>(n) + eps) : 1.0f;
+        __syncwarp();
+        if (kind == 0) {
+            T* dst = q + static_cast<size_t>(row) * ldq + static_cast<size_t>(head) * n;
+            for (int c = lane; c < n; c += 32) mlr_store(dst, c, mine[c] * inv);
+        } else if (kind == 1) {
+            T* dst = kbase + static_cast<size_t>(head) * page_size * s.dim;
+            for (int c = lane; c < n; c += 32) {
+                float value = mine[c] * inv;
+                if (c < s.rot_dims) {
+                    float sn, cs;
+                    sincosf(p * s.freq[c < half ? c : c - half], &sn, &cs);
+                    const float other = mine[c < half ? c + half : c - half] * inv;
+                    value = c < half ? value * cs - other * sn : value * cs + other * sn;
+                }
+                mlr_store(dst, c, value);
+            }
+        } else {
+            T* dst = vbase + static_cast<size_t>(head) * page_size * s.vdim;
+            float* keep = first ? first + static_cast<size_t>(row) * ld_first + static_cast<size_t>(head) * n : nullptr;
+            for (int c = lane; c < n; c += 32) {
+                float value = mine[c] * inv;
+                if (mix == 1) keep[c] = value;
+                else if (mix == 2) value = (1.0f - lambda) * value + lambda * __ldcg(keep + c);
+                mlr_store(dst, c, value);
+            }
+        }
+        __syncwarp();
+    }
+    mlr_grid_dependents_may_start();
+}
+
 template <typename T, int DPT>
 __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, int ldq, const T* gate, int ld_gate, T* out, int ldo,
                                                                     const T* cache, int num_pages, const int* positions,
@@ -107,9 +202,13 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
     int lo = 0;
     if (s.window > 0) lo = max(lo, position - s.window + 1);
     if (s.chunk > 0) lo = max(lo, (position / s.chunk) * s.chunk);
+    const int kept = (s.window > 0 && s.keep_first > 0) ? min(s.keep_first, lo) : 0;       // keys [0, kept) are seen beside [lo, position]
+    const float slope = s.slopes ? s.slopes[head] : 0.0f;
+    const float sink_score = s.sinks ? s.sinks[head] : 0.0f;
     const int* table = block_table + static_cast<size_t>(segment) * table_stride;
     const size_t page_elems = static_cast<size_t>(s.kv_heads) * page_size * (s.shared_kv ? s.dim : s.dim + s.vdim);
     const size_t key_plane = s.shared_kv ? 0 : static_cast<size_t>(s.kv_heads) * page_size * s.dim;
+    const int value_row = s.shared_kv ? s.dim : s.vdim;      // values between two tokens' value rows
 
     const T* qrow = q + static_cast<size_t>(row) * ldq + static_cast<size_t>(head) * s.dim;
     const int half = s.rot_dims / 2;
@@ -130,7 +229,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
     // The sink is a key of score 0 that is always seen and carries no value.  With `partial` the visible keys are cut
     // into ranges of `split_keys` (from the 64-key border at or below the first one); blockIdx.z names this block's
     // range, whose maximum, sum and weighted values go to `partial` for `attention_masked_merge_kernel` (the sink too).
-    float running_max = (s.sink && !partial) ? 0.0f : -INFINITY, running_sum = (s.sink && !partial) ? 1.0f : 0.0f;
+    float running_max = (s.sink && !partial) ? sink_score : -INFINITY, running_sum = (s.sink && !partial) ? 1.0f : 0.0f;
     float acc[DPT] = {};
     int tile_first = (lo / kTile) * kTile, tile_last = position;
     if (partial) {
@@ -141,20 +240,26 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
 
     constexpr int kChunk = 16 / sizeof(T);                      // values in 16 bytes
     const bool chunked_rows = s.dim % kChunk == 0;              // a key's row is whole 16-byte pieces, each aligned
-    for (int tile = tile_first; tile <= tile_last; tile += kTile) {
+    // The kept first keys come first, as tiles of their own (of the first key range only); then the window's tiles.
+    const int kept_tiles = (kept > 0 && (!partial || blockIdx.z == 0)) ? (kept + kTile - 1) / kTile : 0;
+    const int main_tiles = (tile_last - tile_first) / kTile + 1;
+    for (int step = 0; step < kept_tiles + main_tiles; ++step) {
+        const bool early = step < kept_tiles;
+        const int tile = early ? step * kTile : tile_first + (step - kept_tiles) * kTile;
+        const int see_lo = early ? 0 : lo, see_hi = early ? kept - 1 : tile_last;
         if (chunked_rows) {
             // Scores of this tile: two threads per key, each adds up every other 16-byte piece of the key's row.
             const int i = threadIdx.x >> 1, t = tile + i;
             float partial = 0.0f;
             long long offset = -1;
-            if (t >= lo && t <= tile_last) {
+            if (t >= see_lo && t <= see_hi) {
                 const int page = table[t / page_size];
                 if (page < 0 || page >= num_pages) {
                     bad = 1;
                 } else {
                     const T* k = cache + page * page_elems + (static_cast<size_t>(kv_head) * page_size + t % page_size) * s.dim;
                     offset = static_cast<long long>(page * page_elems + key_plane +
-                                                    (static_cast<size_t>(kv_head) * page_size + t % page_size) * s.vdim);
+                                                    (static_cast<size_t>(kv_head) * page_size + t % page_size) * value_row);
                     for (int c0 = (threadIdx.x & 1) * kChunk; c0 < s.dim; c0 += 8 * kChunk) {     // four pieces on their way at a time
                         float v[4][kChunk];
 #pragma unroll
@@ -178,7 +283,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
             }
             partial += __shfl_xor_sync(0xffffffffu, partial, 1);
             if ((threadIdx.x & 1) == 0) {
-                scores[i] = offset >= 0 ? partial * s.scale : -INFINITY;
+                scores[i] = offset >= 0 ? mlr_masked_score(partial, position - t, slope, s) : -INFINITY;
                 offsets[i] = offset;
             }
         } else
@@ -186,17 +291,17 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
             const int t = tile + i;
             float score = -INFINITY;
             long long offset = -1;
-            if (t >= lo && t <= tile_last) {
+            if (t >= see_lo && t <= see_hi) {
                 const int page = table[t / page_size];
                 if (page < 0 || page >= num_pages) {
                     if (lane == 0) bad = 1;
                 } else {
                     const T* k = cache + page * page_elems + (static_cast<size_t>(kv_head) * page_size + t % page_size) * s.dim;
                     offset = static_cast<long long>(page * page_elems + key_plane +
-                                                    (static_cast<size_t>(kv_head) * page_size + t % page_size) * s.vdim);
+                                                    (static_cast<size_t>(kv_head) * page_size + t % page_size) * value_row);
                     float partial = 0.0f;
                     for (int j = lane; j < s.dim; j += 32) partial = fmaf(qs[j], mlr_load(k, j), partial);
-                    score = mlr_warp_sum(partial) * s.scale;
+                    score = mlr_masked_score(mlr_warp_sum(partial), position - t, slope, s);
                 }
             }
             if (lane == 0) {
@@ -258,17 +363,13 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
         return;
     }
     T* orow = out + static_cast<size_t>(row) * ldo + static_cast<size_t>(head) * s.vdim;
-    const T* grow = gate ? gate + static_cast<size_t>(row) * ld_gate + static_cast<size_t>(head) * s.vdim : nullptr;
+    const T* grow = gate ? gate + static_cast<size_t>(row) * ld_gate + static_cast<size_t>(head) * (s.gate_kind == 3 ? 1 : s.vdim) : nullptr;
 #pragma unroll
     for (int d = 0; d < DPT; ++d) {
         const int c = threadIdx.x + d * kThreads;
         if (c < s.vdim) {
             float value = running_sum > 0.0f ? acc[d] / running_sum : 0.0f;
-            if (grow) {
-                const float g = mlr_load(grow, c);
-                const float sig = 1.0f / (1.0f + expf(-g));
-                value *= s.gate_kind == 2 ? g * sig : sig;
-            }
+            if (grow) value *= mlr_gate_value(mlr_load(grow, s.gate_kind == 3 ? 0 : c), s.gate_kind);
             mlr_store(orow, c, value * s.out_scale);
         }
     }
@@ -293,9 +394,10 @@ __global__ void __launch_bounds__(kThreads) attention_masked_merge_kernel(const 
     if (s.chunk > 0) lo = max(lo, (position / s.chunk) * s.chunk);
     const int splits = (position - (lo / kTile) * kTile) / split_keys + 1;
     const float* mine = partial + (static_cast<size_t>(item) * kRowsPerItem * s.kv_heads + j * s.heads + head) * max_splits * (s.vdim + 2);
-    float top = s.sink ? 0.0f : -INFINITY;
+    const float sink_score = s.sinks ? s.sinks[head] : 0.0f;
+    float top = s.sink ? sink_score : -INFINITY;
     for (int i = 0; i < splits; ++i) top = fmaxf(top, __ldcg(mine + static_cast<size_t>(i) * (s.vdim + 2)));
-    float sum = s.sink ? expf(-top) : 0.0f;
+    float sum = s.sink ? expf(sink_score - top) : 0.0f;
     float acc[DPT] = {};
     for (int i = 0; i < splits; ++i) {
         const float* part = mine + static_cast<size_t>(i) * (s.vdim + 2);
@@ -310,17 +412,13 @@ __global__ void __launch_bounds__(kThreads) attention_masked_merge_kernel(const 
         }
     }
     T* orow = out + static_cast<size_t>(row) * ldo + static_cast<size_t>(head) * s.vdim;
-    const T* grow = gate ? gate + static_cast<size_t>(row) * ld_gate + static_cast<size_t>(head) * s.vdim : nullptr;
+    const T* grow = gate ? gate + static_cast<size_t>(row) * ld_gate + static_cast<size_t>(head) * (s.gate_kind == 3 ? 1 : s.vdim) : nullptr;
 #pragma unroll
     for (int d = 0; d < DPT; ++d) {
         const int c = threadIdx.x + d * kThreads;
         if (c < s.vdim) {
             float value = sum > 0.0f ? acc[d] / sum : 0.0f;
-            if (grow) {
-                const float g = mlr_load(grow, c);
-                const float sig = 1.0f / (1.0f + expf(-g));
-                value *= s.gate_kind == 2 ? g * sig : sig;
-            }
+            if (grow) value *= mlr_gate_value(mlr_load(grow, s.gate_kind == 3 ? 0 : c), s.gate_kind);
             mlr_store(orow, c, value * s.out_scale);
         }
     }
@@ -387,6 +485,11 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
     const int* table = block_table + static_cast<size_t>(segment) * table_stride;
     const size_t page_elems = static_cast<size_t>(s.kv_heads) * page_size * (s.shared_kv ? s.dim : s.dim + s.vdim);
     const size_t key_plane = s.shared_kv ? 0 : static_cast<size_t>(s.kv_heads) * page_size * s.dim;
+    const int value_row = s.shared_kv ? s.dim : s.vdim;
+    const int keep_first = s.window > 0 ? s.keep_first : 0;
+    const float slope = s.slopes ? s.slopes[head] : 0.0f;
+    const float sink_score = s.sinks ? s.sinks[head] : 0.0f;
+    const bool plain_scores = !(s.softcap > 0.0f) && !s.slopes;
     if (threadIdx.x == 0) bad = 0;
 
     // The block's queries, rotated in float32, as bfloat16.
@@ -411,7 +514,7 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
     const int pos_a = first_pos + r0 + g, pos_b = pos_a + 8;         // this thread's two rows
     const bool row_a = r0 + g < n_rows, row_b = r0 + g + 8 < n_rows;
     const int lo_a = first_visible(pos_a, s), lo_b = first_visible(pos_b, s);
-    float m_a = s.sink ? 0.0f : -INFINITY, m_b = m_a, l_a = s.sink ? 1.0f : 0.0f, l_b = l_a;   // l: this thread's share, but the sink's 1
+    float m_a = s.sink ? sink_score : -INFINITY, m_b = m_a, l_a = s.sink ? 1.0f : 0.0f, l_b = l_a;   // l: this thread's share, but the sink's 1
     if (t != 0) l_a = l_b = 0.0f;                                                                // is counted once per row
     float O[NV][4];
 #pragma unroll
@@ -429,7 +532,7 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
         // Two threads per key: the page and the row's addresses once, then every other 16-byte piece of the key's row
         // and of its value row.
         const int key = threadIdx.x >> 1, position = kt + key;
-        bool real = position >= lo_min && position <= last_pos;
+        bool real = position <= last_pos && (position >= lo_min || position < keep_first);
         const __nv_bfloat16* ksrc = cache;
         const __nv_bfloat16* vsrc = cache;
         if (real) {
@@ -440,7 +543,7 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
             } else {
                 const size_t in_page = static_cast<size_t>(kv_head) * page_size + position % page_size;
                 ksrc = cache + page * page_elems + in_page * s.dim;
-                vsrc = cache + page * page_elems + key_plane + in_page * s.vdim;
+                vsrc = cache + page * page_elems + key_plane + in_page * value_row;
             }
         }
         __nv_bfloat16* krow = kdst + key * qstride;
@@ -449,13 +552,19 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
         for (int c = (threadIdx.x & 1) * 8; c < s.vdim; c += 16) mlr_async_copy16(vrow + c, real ? vsrc + c : cache, real);
         mlr_async_commit();
     };
+    // Tiles of keys in the order they are walked: those of the kept first tokens that lie before the window's first tile, then
+    // the window's tiles up to the block's last position.
     const int kt_first = (lo_min / kKeys) * kKeys;
-    fetch(kt_first, 0);
+    const int early_tiles = (min(keep_first, kt_first) + kKeys - 1) / kKeys;
+    const int all_tiles = early_tiles + (last_pos - kt_first) / kKeys + 1;
+    auto tile_start = [&](int i) { return i < early_tiles ? i * kKeys : kt_first + (i - early_tiles) * kKeys; };
+    fetch(tile_start(0), 0);
     int current = 0;
-    for (int kt = kt_first; kt <= last_pos; kt += kKeys, current ^= 1) {
+    for (int ti = 0; ti < all_tiles; ++ti, current ^= 1) {
+        const int kt = tile_start(ti);
         mlr_async_wait();
         __syncthreads();      // this tile has arrived (and Qs is written); no warp still reads the other stage
-        if (kt + kKeys <= last_pos) fetch(kt + kKeys, current ^ 1);
+        if (ti + 1 < all_tiles) fetch(tile_start(ti + 1), current ^ 1);
         const uint32_t kt_base = ks_base + static_cast<uint32_t>(current * kKeys * qstride * 2);
         const uint32_t vt_base = vs_base + static_cast<uint32_t>(current * kKeys * vstride * 2);
         float S[8][4];
@@ -490,13 +599,23 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
         float tile_a = -INFINITY, tile_b = -INFINITY;
         const int warp_first = first_pos + r0, warp_last = warp_first + 15;
         const bool open = r0 + 15 < n_rows && kt + kKeys - 1 <= warp_first && kt >= first_visible(warp_last, s);
-        if (open) {
+        if (open && plain_scores) {
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
                 S[nt][0] *= s.scale; S[nt][1] *= s.scale; S[nt][2] *= s.scale; S[nt][3] *= s.scale;
                 tile_a = fmaxf(tile_a, fmaxf(S[nt][0], S[nt][1]));
                 tile_b = fmaxf(tile_b, fmaxf(S[nt][2], S[nt][3]));
             }
+        } else if (open) {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = kt + nt * 8 + 2 * t + (e & 1);
+                    const float v = mlr_masked_score(S[nt][e], (e < 2 ? pos_a : pos_b) - key, slope, s);
+                    S[nt][e] = v;
+                    if (e < 2) tile_a = fmaxf(tile_a, v); else tile_b = fmaxf(tile_b, v);
+                }
         } else {
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt)
@@ -504,8 +623,9 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
                 for (int e = 0; e < 4; ++e) {
                     const int key = kt + nt * 8 + 2 * t + (e & 1);
                     const bool upper = e < 2;
-                    const bool seen = upper ? (row_a && key <= pos_a && key >= lo_a) : (row_b && key <= pos_b && key >= lo_b);
-                    const float v = seen ? S[nt][e] * s.scale : -INFINITY;
+                    const bool seen = upper ? (row_a && key <= pos_a && (key >= lo_a || key < keep_first))
+                                            : (row_b && key <= pos_b && (key >= lo_b || key < keep_first));
+                    const float v = seen ? mlr_masked_score(S[nt][e], (upper ? pos_a : pos_b) - key, slope, s) : -INFINITY;
                     S[nt][e] = v;
                     if (upper) tile_a = fmaxf(tile_a, v); else tile_b = fmaxf(tile_b, v);
                 }
@@ -575,11 +695,13 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
             const float l = hb ? l_b : l_a;
             float v0 = l > 0.0f ? O[nv][2 * hb] / l : 0.0f, v1 = l > 0.0f ? O[nv][2 * hb + 1] / l : 0.0f;
             const size_t row = static_cast<size_t>(first + tile_token + r0 + g + 8 * hb);
-            if (gate) {
-                const float g0 = __bfloat162float(gate[row * ld_gate + col]), g1 = __bfloat162float(gate[row * ld_gate + col + 1]);
-                const float s0 = 1.0f / (1.0f + expf(-g0)), s1 = 1.0f / (1.0f + expf(-g1));
-                v0 *= s.gate_kind == 2 ? g0 * s0 : s0;
-                v1 *= s.gate_kind == 2 ? g1 * s1 : s1;
+            if (gate && s.gate_kind == 3) {
+                const float one = mlr_gate_value(__bfloat162float(gate[row * ld_gate + head]), 3);
+                v0 *= one;
+                v1 *= one;
+            } else if (gate) {
+                v0 *= mlr_gate_value(__bfloat162float(gate[row * ld_gate + col]), s.gate_kind);
+                v1 *= mlr_gate_value(__bfloat162float(gate[row * ld_gate + col + 1]), s.gate_kind);
             }
             *reinterpret_cast<__nv_bfloat162*>(out + row * ldo + col) = __floats2bfloat162_rn(v0 * s.out_scale, v1 * s.out_scale);
         }
@@ -596,7 +718,9 @@ int check_spec(const MaskedAttentionSpec* s, const char* who) {
     MLR_REQUIRE(s->rot_dims >= 0 && s->rot_dims % 2 == 0 && s->rot_dims <= s->dim && (s->rot_dims == 0 || s->freq),
                 "%s: %d rotated values do not fit a head of %d (or no frequencies were given)", who, s->rot_dims, s->dim);
     MLR_REQUIRE(s->window >= 0 && s->chunk >= 0 && s->heads <= 65535, "%s: bad window, chunk or head count", who);
-    MLR_REQUIRE(!s->shared_kv || s->vdim == s->dim, "%s: values that are the keys have the keys' size, not %d against %d", who, s->vdim, s->dim);
+    MLR_REQUIRE(!s->shared_kv || s->vdim <= s->dim, "%s: values that are the start of their keys cannot be longer, %d against %d", who, s->vdim, s->dim);
+    MLR_REQUIRE(s->keep_first >= 0 && (s->keep_first == 0 || (s->window > 0 && s->chunk == 0)), "%s: kept first tokens go with a window and without chunks", who);
+    MLR_REQUIRE(s->gate_kind >= 0 && s->gate_kind <= 3 && (!s->sinks || s->sink), "%s: bad gate kind, or sink scores without a sink", who);
     return 0;
 }
 
@@ -618,6 +742,32 @@ MLR_API int mlr_kv_rope_cache(const MaskedAttentionSpec* spec, const void* k, in
                    static_cast<const float*>(v), ld_v, static_cast<float*>(cache), num_pages, positions, segment_of_row, block_table,
                    table_stride, page_size, *spec, status);
     return mlr_launched("kv_rope_cache");
+}
+
+// q, k, v: the step's projections (q is changed in place); bq, bk, bv: float32 biases or null; first: float32 [rows, kv_heads * vdim]
+// (row stride ld_first) with mix 1 (written) or 2 (read), else null.  Not for caches whose values are their keys.
+MLR_API int mlr_qkv_prepare_cache(const MaskedAttentionSpec* spec, void* q, int ldq, const void* k, int ld_k, const void* v, int ld_v, int act_bf16,
+                                  const float* bq, const float* bk, const float* bv, int unit_qk, int unit_v, float eps, float* first, int ld_first,
+                                  int mix, float lambda, void* cache, int num_pages, const int* positions, const int* segment_of_row,
+                                  const int* block_table, int table_stride, int page_size, int rows, int* status, cudaStream_t stream) {
+    if (check_spec(spec, "qkv_prepare_cache")) return 1;
+    MLR_REQUIRE(rows >= 0 && page_size > 0 && num_pages > 0 && cache && block_table && q && k && v, "qkv_prepare_cache: bad sizes or no cache");
+    MLR_REQUIRE(!spec->shared_kv, "qkv_prepare_cache: this cache keeps keys and values apart");
+    MLR_REQUIRE(ldq >= spec->heads * spec->dim && ld_k >= spec->kv_heads * spec->dim && ld_v >= spec->kv_heads * spec->vdim,
+                "qkv_prepare_cache: a row stride is smaller than the row");
+    MLR_REQUIRE(mix >= 0 && mix <= 2 && (mix == 0 || (first && ld_first >= spec->kv_heads * spec->vdim)), "qkv_prepare_cache: mixing needs the first values' buffer");
+    if (rows == 0) return 0;
+    const size_t shared = sizeof(float) * (kThreads / 32) * static_cast<size_t>(spec->dim > spec->vdim ? spec->dim : spec->vdim);
+    if (act_bf16)
+        mlr_launch((qkv_prepare_cache_kernel<__nv_bfloat16>), dim3(rows), dim3(kThreads), shared, stream, static_cast<__nv_bfloat16*>(q), ldq,
+                   static_cast<const __nv_bfloat16*>(k), ld_k, static_cast<const __nv_bfloat16*>(v), ld_v, bq, bk, bv, unit_qk, unit_v, eps, first,
+                   ld_first, mix, lambda, static_cast<__nv_bfloat16*>(cache), num_pages, positions, segment_of_row, block_table, table_stride,
+                   page_size, *spec, status);
+    else
+        mlr_launch((qkv_prepare_cache_kernel<float>), dim3(rows), dim3(kThreads), shared, stream, static_cast<float*>(q), ldq,
+                   static_cast<const float*>(k), ld_k, static_cast<const float*>(v), ld_v, bq, bk, bv, unit_qk, unit_v, eps, first, ld_first, mix,
+                   lambda, static_cast<float*>(cache), num_pages, positions, segment_of_row, block_table, table_stride, page_size, *spec, status);
+    return mlr_launched("qkv_prepare_cache");
 }
 
 MLR_API int mlr_attention_masked(const MaskedAttentionSpec* spec, const void* q, int ldq, const void* gate, int ld_gate, void* out,

@@ -438,9 +438,26 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 
 // Gated activation with biases: out = act(gate + b_gate) * (up + b_up), gate in the first `inter` columns of a row
 // and up in the next `inter`; act is SiLU (0) or the tanh form of GELU (1).  Biases are float32, may be null.
+// The gate's shape.  activation 0: silu(g) * u.  1: gelu_tanh(g) * u.  2: with limit > 0 first g <- min(g, limit) and
+// u <- clamp(u, -limit, limit); then g * sigmoid(alpha * g) * (u + up_offset).
+struct GateShape {
+    float alpha, limit, up_offset;
+};
+__device__ __forceinline__ float gated_value(float g, float u, int activation, const GateShape& shape) {
+    if (activation == 2) {
+        if (shape.limit > 0.0f) {
+            g = fminf(g, shape.limit);
+            u = fminf(fmaxf(u, -shape.limit), shape.limit);
+        }
+        return g / (1.0f + expf(-shape.alpha * g)) * (u + shape.up_offset);
+    }
+    const float a = activation == 1 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.0f + expf(-g));
+    return a * u;
+}
+
 template <typename T>
 __global__ void gated_bias_kernel(const T* gate_up, int ld, const float* bias_gate, const float* bias_up, T* out, int ld_out,
-                                  int rows, int inter, int activation) {
+                                  int rows, int inter, int activation, GateShape shape) {
     mlr_grid_wait();
     const size_t total = static_cast<size_t>(rows) * inter;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -448,9 +465,7 @@ __global__ void gated_bias_kernel(const T* gate_up, int ld, const float* bias_ga
         const size_t r = i / inter, c = i - r * inter;
         const float g = mlr_load(gate_up, r * ld + c) + (bias_gate ? bias_gate[c] : 0.0f);
         const float u = mlr_load(gate_up, r * ld + inter + c) + (bias_up ? bias_up[c] : 0.0f);
-        const float a = activation == 1 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
-                                        : g / (1.0f + expf(-g));
-        mlr_store(out, r * ld_out + c, a * u);
+        mlr_store(out, r * ld_out + c, gated_value(g, u, activation, shape));
     }
     mlr_grid_dependents_may_start();
 }
@@ -649,7 +664,7 @@ MLR_API int mlr_swiglu(const void* gate_up, void* out, int act_bf16, int rows, i
 // The same, eight consecutive columns a thread (all row starts and `inter` on 16-byte borders).  grid = (column blocks, rows).
 template <typename T>
 __global__ void gated_bias_vec8_kernel(const T* gate_up, int ld, const float* bias_gate, const float* bias_up, T* out, int ld_out,
-                                       int inter, int activation) {
+                                       int inter, int activation, GateShape shape) {
     mlr_grid_wait();
     const int q = blockIdx.x * blockDim.x + threadIdx.x;
     if (q < (inter >> 3)) {
@@ -661,19 +676,21 @@ __global__ void gated_bias_vec8_kernel(const T* gate_up, int ld, const float* bi
         for (int e = 0; e < 8; ++e) {
             const float z = g[e] + (bias_gate ? bias_gate[c + e] : 0.0f);
             const float up = u[e] + (bias_up ? bias_up[c + e] : 0.0f);
-            const float a = activation == 1 ? 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)))
-                                            : z / (1.0f + expf(-z));
-            o[e] = a * up;
+            o[e] = gated_value(z, up, activation, shape);
         }
         mlr_store8(out + r * ld_out + c, o);
     }
     mlr_grid_dependents_may_start();
 }
 
-MLR_API int mlr_gated_bias(const void* gate_up, int ld, const float* bias_gate, const float* bias_up, void* out, int ld_out,
-                           int act_bf16, int rows, int inter, int activation, cudaStream_t stream) {
+// gate_up: [rows, 2 * inter] (gate columns, then up columns; row stride ld); biases float32 [inter] or null; `activation` and the
+// three constants as `GateShape` says.
+MLR_API int mlr_gated_bias_shaped(const void* gate_up, int ld, const float* bias_gate, const float* bias_up, void* out, int ld_out,
+                                  int act_bf16, int rows, int inter, int activation, float alpha, float limit, float up_offset,
+                                  cudaStream_t stream) {
     MLR_REQUIRE(rows >= 0 && inter > 0 && ld >= 2 * inter && ld_out >= inter, "gated_bias: bad sizes rows=%d inter=%d", rows, inter);
-    MLR_REQUIRE(activation == 0 || activation == 1, "gated_bias: unknown activation %d", activation);
+    MLR_REQUIRE(activation >= 0 && activation <= 2, "gated_bias: unknown activation %d", activation);
+    const GateShape shape = {alpha, limit, up_offset};
     if (rows == 0) return 0;
     const int unit = act_bf16 ? 8 : 4;          // values in 16 bytes
     if (inter % 8 == 0 && ld % unit == 0 && ld_out % unit == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 &&
@@ -681,20 +698,26 @@ MLR_API int mlr_gated_bias(const void* gate_up, int ld, const float* bias_gate, 
         const dim3 grid((inter / 8 + 127) / 128, rows);
         if (act_bf16)
             mlr_launch((gated_bias_vec8_kernel<__nv_bfloat16>), dim3(grid), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(gate_up),
-                       ld, bias_gate, bias_up, static_cast<__nv_bfloat16*>(out), ld_out, inter, activation);
+                       ld, bias_gate, bias_up, static_cast<__nv_bfloat16*>(out), ld_out, inter, activation, shape);
         else
             mlr_launch((gated_bias_vec8_kernel<float>), dim3(grid), dim3(128), 0, stream, static_cast<const float*>(gate_up), ld, bias_gate,
-                       bias_up, static_cast<float*>(out), ld_out, inter, activation);
+                       bias_up, static_cast<float*>(out), ld_out, inter, activation, shape);
         return mlr_launched("gated_bias");
     }
     const int blocks = mlr_grid_stride_blocks(static_cast<size_t>(rows) * inter / 1024 + 1, 16);
     if (act_bf16)
         mlr_launch((gated_bias_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(gate_up), ld,
-                   bias_gate, bias_up, static_cast<__nv_bfloat16*>(out), ld_out, rows, inter, activation);
+                   bias_gate, bias_up, static_cast<__nv_bfloat16*>(out), ld_out, rows, inter, activation, shape);
     else
         mlr_launch((gated_bias_kernel<float>), dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(gate_up), ld, bias_gate,
-                   bias_up, static_cast<float*>(out), ld_out, rows, inter, activation);
+                   bias_up, static_cast<float*>(out), ld_out, rows, inter, activation, shape);
     return mlr_launched("gated_bias");
+}
+
+MLR_API int mlr_gated_bias(const void* gate_up, int ld, const float* bias_gate, const float* bias_up, void* out, int ld_out,
+                           int act_bf16, int rows, int inter, int activation, cudaStream_t stream) {
+    MLR_REQUIRE(activation == 0 || activation == 1, "gated_bias: unknown activation %d", activation);
+    return mlr_gated_bias_shaped(gate_up, ld, bias_gate, bias_up, out, ld_out, act_bf16, rows, inter, activation, 1.0f, 0.0f, 0.0f, stream);
 }
 
 // The same from `slices` float32 partial sums of the stacked product [slices][rows][2 * inter].

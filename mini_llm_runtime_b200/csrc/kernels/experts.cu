@@ -522,10 +522,11 @@ MLR_API int mlr_experts_product(const void* a, long long lda, int act_bf16, cons
 
 // The same tensor-core product for `count` matrices that all take the same rows (the heads of a per-head projection):
 // out[m, i * N + n] = sum_k a[m, i * K + k] w[i, n, k], bfloat16 in and out.  Returns 2 (and launches nothing) for sizes it does not take.
-MLR_API int mlr_batched_product_bf16(const void* a, long long lda, const void* w, void* out, long long ldo, int rows, int count, int N, int K,
-                                     cudaStream_t stream) {
-    MLR_REQUIRE(a && w && out && count > 0 && count <= 65535 && N > 0 && K > 0, "batched_product: bad arguments");
-    if (K % 8 || lda % 8 || reinterpret_cast<uintptr_t>(a) % 16 || reinterpret_cast<uintptr_t>(w) % 16 || mlr_experts_simt_only()) return 2;
+// With a_step and out_step matrix i reads its K inputs from column i * a_step and writes its N outputs from column i * out_step.
+MLR_API int mlr_batched_product_bf16_strided(const void* a, long long lda, int a_step, const void* w, void* out, long long ldo, int out_step, int rows,
+                                             int count, int N, int K, cudaStream_t stream) {
+    MLR_REQUIRE(a && w && out && count > 0 && count <= 65535 && N > 0 && K > 0 && a_step >= K && out_step >= N, "batched_product: bad arguments");
+    if (K % 8 || lda % 8 || a_step % 8 || reinterpret_cast<uintptr_t>(a) % 16 || reinterpret_cast<uintptr_t>(w) % 16 || mlr_experts_simt_only()) return 2;
     if (rows <= 0) return 0;
     const __nv_bfloat16 *ab = static_cast<const __nv_bfloat16*>(a), *wb = static_cast<const __nv_bfloat16*>(w);
     const int* none = nullptr;
@@ -535,15 +536,20 @@ MLR_API int mlr_batched_product_bf16(const void* a, long long lda, const void* w
         cudaFuncSetAttribute(expert_product_mma_kernel<__nv_bfloat16, false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(mma_shared_bytes(64, false)));
         mlr_launch((expert_product_mma_kernel<__nv_bfloat16, false, 64>), dim3(grid), dim3(256), mma_shared_bytes(64, false), stream, ab, lda, none, 1,
-                   wb, wb, N, K, static_cast<__nv_bfloat16*>(out), ldo, none, none, rows, K, N);
+                   wb, wb, N, K, static_cast<__nv_bfloat16*>(out), ldo, none, none, rows, a_step, out_step);
     } else {
         const dim3 grid((N + kMmaCols - 1) / kMmaCols, 1, count);
         cudaFuncSetAttribute(expert_product_mma_kernel<__nv_bfloat16, false, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(mma_shared_bytes(32, false)));
         mlr_launch((expert_product_mma_kernel<__nv_bfloat16, false, 32>), dim3(grid), dim3(256), mma_shared_bytes(32, false), stream, ab, lda, none, 1,
-                   wb, wb, N, K, static_cast<__nv_bfloat16*>(out), ldo, none, none, rows, K, N);
+                   wb, wb, N, K, static_cast<__nv_bfloat16*>(out), ldo, none, none, rows, a_step, out_step);
     }
     return mlr_launched("batched_product");
+}
+
+MLR_API int mlr_batched_product_bf16(const void* a, long long lda, const void* w, void* out, long long ldo, int rows, int count, int N, int K,
+                                     cudaStream_t stream) {
+    return mlr_batched_product_bf16_strided(a, lda, K, w, out, ldo, N, rows, count, N, K, stream);
 }
 
 MLR_API int mlr_experts_combine(const float* y, long long ldy, const int* row_of_pair, const float* weights, int top, const void* shared_y,

@@ -155,6 +155,14 @@ class EagerBuilder(_NormHints):
     def logits(self, vocab: int) -> Buf:
         return self.temp(self.want, vocab, torch.float32)
 
+    def kept(self, key, rows: Count, width: int, dtype: torch.dtype, slices: int = 0) -> Buf:
+        """A buffer that lives for the whole step and that every part asking for `key` gets: what one layer leaves
+        for later layers of the same step (the first call makes it)."""
+        found = self.step.scratch.get(("kept", key))
+        if found is None:
+            found = self.step.scratch[("kept", key)] = self.temp(rows, width, dtype, slices)
+        return found
+
     # ---- what the step knows
     def meta(self, name: str) -> int:
         if name == "want_rows":
@@ -250,6 +258,7 @@ class ProgramBuilder(_NormHints):
         self._bank = 0
         self._in_banks = False
         self.bank_bytes = [0, 0]
+        self._kept: Dict[object, Buf] = {}
 
     # ---- decisions on a row count: they must hold for the program's whole range
     def _range(self, count: Count):
@@ -316,6 +325,18 @@ class ProgramBuilder(_NormHints):
 
     def logits(self, vocab: int) -> Buf:
         return Buf(Sym(K_LOGITS), self.want, vocab, torch.float32, vocab)
+
+    def kept(self, key, rows: Count, width: int, dtype: torch.dtype, slices: int = 0) -> Buf:
+        """A buffer that lives for the whole step and that every part asking for `key` gets (cut from the fixed part of the
+        workspace, not from the banks that alternate run by run)."""
+        found = self._kept.get(key)
+        if found is None:
+            in_banks, self._in_banks = self._in_banks, False
+            try:
+                found = self._kept[key] = self.temp(rows, width, dtype, slices)
+            finally:
+                self._in_banks = in_banks
+        return found
 
     def wrap(self, t):
         raise RuntimeError("a program is built from the parts' own buffers, not from tensors")

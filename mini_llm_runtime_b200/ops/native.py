@@ -35,6 +35,8 @@ _SIGNATURES = {
                                    c_void_p, c_int, c_int, c_void_p, c_void_p],
         "mlr_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mlr_gated_bias": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "mlr_gated_bias_shaped": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float,
+                                  c_void_p],
     },
     "gemm_f32": {
         "mlr_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -87,7 +89,14 @@ _SIGNATURES = {
         "mlr_group_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                               c_int, c_float, c_int, c_void_p],
     },
+    "layernorm": {
+        "mlr_depth_norm": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
+                           c_void_p, c_float, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    },
     "attention_masked": {
+        "mlr_qkv_prepare_cache": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                  c_float, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                  c_void_p, c_void_p],
         "mlr_kv_rope_cache": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                               c_int, c_int, c_void_p, c_void_p],
         "mlr_attention_masked": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
@@ -115,6 +124,10 @@ _SIGNATURES = {
         "mlr_latent_cache": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                              c_int, c_int, c_int, c_void_p, c_void_p],
         "mlr_head_project": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "mlr_head_project_strided": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "mlr_latent_rot_cache": [c_void_p, c_longlong, c_int, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int,
+                                 c_int, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                 c_int, c_void_p, c_void_p],
     },
     "experts": {
         "mlr_experts_route": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
@@ -123,6 +136,7 @@ _SIGNATURES = {
                                 c_void_p],
         "mlr_experts_tensor_cores": [c_int, c_longlong],
         "mlr_batched_product_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p],
+        "mlr_batched_product_bf16_strided": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mlr_experts_max_tiles": [c_int, c_int],
         "mlr_experts_product": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                 c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],

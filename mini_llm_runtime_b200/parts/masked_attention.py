@@ -15,6 +15,20 @@ Parameters: hidden_size, num_heads, num_kv_heads, head_dim, value_dim, scale, wi
 (None or n), sink (bool), gate (None | "sigmoid" | "silu"), position (name of a `rotary_frequencies`
 encoding of the plan, or None).  Weights: "q" [H D, W], "k" [G D, W], "v" [G Dv, W], "g" [H Dv, W] (with a
 gate), "o" [W, H Dv].
+
+Further parameters, all off unless named (with any of the first four the step's q, k and v go through
+`mlr_qkv_prepare_cache` instead of `mlr_kv_rope_cache`):
+    bias        q, k and v have biases: weights "q_bias" [H D], "k_bias" [G D], "v_bias" [G Dv]
+    unit_qk     each head of q and of k is divided by its root mean square (eps `eps`, no weight)
+    unit_v      each head of v likewise; the cache holds the divided values
+    value_mix   "first": this layer's values (after the division) are kept for the step;  "later": v <- (1 - l) v + l v_first with
+                v_first what the "first" layer kept for the same token and l the weight "vmix" (a single number); the mixed values are
+                cached.  Both kinds name the weight (a checkpoint stores it for the first layer too, which does not read it).
+    keep_first  with a window: the first keep_first positions of a sequence stay visible (the cache then keeps every page)
+    softcap     score <- softcap * tanh(score / softcap)
+    slopes      one number per head: score -= slope_h * (query position - key position)
+    sink        "learned": the sink's score is a weight per head ("sink" [H]) instead of 0
+    gate        "sigmoid_head": one gate value per head ("g" [H, W])
 """
 from __future__ import annotations
 
@@ -42,7 +56,22 @@ class MaskedAttentionMixer(SequenceCore):
         self.scale = float(p["scale"])
         self.window, self.chunk = p.get("window"), p.get("chunk")
         self.sink = bool(p.get("sink", False))
+        self.learned_sink = p.get("sink") == "learned"
         self.gate = p.get("gate")
+        self.bias, self.unit_qk, self.unit_v = bool(p.get("bias", False)), bool(p.get("unit_qk", False)), bool(p.get("unit_v", False))
+        self.eps = float(p.get("eps", 0.0))
+        self.value_mix = p.get("value_mix")
+        self.keep_first = int(p.get("keep_first") or 0)
+        self.softcap = float(p.get("softcap") or 0.0)
+        self.slopes = [float(v) for v in p["slopes"]] if p.get("slopes") is not None else None
+        if self.value_mix not in (None, "first", "later"):
+            raise ConfigError(f"unknown value mixing {self.value_mix!r}")
+        if self.keep_first and (self.window is None or self.chunk is not None):
+            raise ConfigError("kept first tokens go with a window and without chunks")
+        if self.slopes is not None and len(self.slopes) != self.heads:
+            raise ConfigError(f"{len(self.slopes)} distance slopes for {self.heads} heads")
+        if (self.unit_qk or self.unit_v) and self.eps <= 0:
+            raise ConfigError("dividing heads by their root mean square needs a positive eps")
         self.position_name = p.get("position")
         self.position = None
         if self.heads % self.kv_heads:
@@ -58,15 +87,37 @@ class MaskedAttentionMixer(SequenceCore):
     def attach_positions(self, positions) -> None:
         if self.position_name is not None:
             self.position = positions[self.position_name]
+            if getattr(self.position, "interleaved", False):
+                raise ConfigError("the masked attention kernels pair value i with value i + dims / 2; an interleaved rotation is not built there")
             if self.position.dims > self.dim:
                 raise ConfigError(f"{self.position.dims} rotated values do not fit a head of {self.dim}")
 
     def cache_need(self) -> CacheNeed:
-        return CacheNeed(self.window, self.kv_heads, self.dim, self.vdim)
+        # Kept first tokens lie before the window: such a cache gives no pages back (the window is then a mask only).
+        return CacheNeed(None if self.keep_first else self.window, self.kv_heads, self.dim, self.vdim)
 
     def in_roles(self) -> List[Tuple[str, int]]:
         roles = [("q", self.heads * self.dim), ("k", self.kv_heads * self.dim), ("v", self.kv_heads * self.vdim)]
-        return roles + ([("g", self.heads * self.vdim)] if self.gate else [])
+        if self.gate:
+            roles.append(("g", self.heads if self.gate == "sigmoid_head" else self.heads * self.vdim))
+        return roles
+
+    def extra_weight_specs(self):
+        from ..weights.loader import WeightSpec
+        w, specs = self.spec.weights, []
+        if self.bias:
+            specs += [WeightSpec(w["q_bias"], (self.heads * self.dim,), "vector", ("normal", 0.02)),
+                      WeightSpec(w["k_bias"], (self.kv_heads * self.dim,), "vector", ("normal", 0.02)),
+                      WeightSpec(w["v_bias"], (self.kv_heads * self.vdim,), "vector", ("normal", 0.02))]
+        if self.value_mix is not None:
+            specs.append(WeightSpec(w["vmix"], (), "vector", ("normal", 0.3)))
+        if self.learned_sink:
+            specs.append(WeightSpec(w["sink"], (self.heads,), "vector", ("normal", 0.5)))
+        return specs
+
+    @property
+    def _prepares(self) -> bool:
+        return self.bias or self.unit_qk or self.unit_v or self.value_mix is not None
 
     def core_width(self) -> int:
         return self.heads * self.vdim
@@ -77,10 +128,19 @@ class MaskedAttentionMixer(SequenceCore):
     def bind_core(self, tensors, rt, out_scale: float) -> None:
         freq = self.position.frequencies() if self.position is not None else None
         self._freq = freq
+        w = self.spec.weights
+        f32 = lambda t: t.to(device=rt.device, dtype=torch.float32).contiguous()
+        self._sinks = f32(rt.vector(tensors[w["sink"]])) if self.learned_sink else None
+        self._slopes = torch.tensor(self.slopes, dtype=torch.float32, device=rt.device) if self.slopes is not None else None
+        self._biases = [f32(rt.vector(tensors[w[r]])) for r in ("q_bias", "k_bias", "v_bias")] if self.bias else [None] * 3
+        self._lambda = float(tensors[w["vmix"]].float().item()) if self.value_mix == "later" else 0.0
         self.desc = MaskedAttentionSpec(
-            freq=freq.data_ptr() if freq is not None and freq.numel() else None, heads=self.heads, kv_heads=self.kv_heads, dim=self.dim,
+            freq=freq.data_ptr() if freq is not None and freq.numel() else None,
+            sinks=self._sinks.data_ptr() if self._sinks is not None else None,
+            slopes=self._slopes.data_ptr() if self._slopes is not None else None, heads=self.heads, kv_heads=self.kv_heads, dim=self.dim,
             vdim=self.vdim, rot_dims=self.position.dims if self.position is not None else 0, window=self.window or 0,
-            chunk=self.chunk or 0, sink=int(self.sink), gate_kind=GATES[self.gate], scale=self.scale, out_scale=float(out_scale))
+            chunk=self.chunk or 0, sink=int(self.sink), gate_kind=GATES[self.gate], keep_first=self.keep_first, scale=self.scale,
+            out_scale=float(out_scale), softcap=self.softcap)
 
     def emit_core(self, b, proj, act, run: RunContext) -> None:
         if run.cache is None or run.cache.dtype is not proj.dtype:
@@ -88,9 +148,21 @@ class MaskedAttentionMixer(SequenceCore):
         at = self.in_columns()
         k = columns_of(proj, at["k"], self.kv_heads * self.dim)
         v = columns_of(proj, at["v"], self.kv_heads * self.vdim)
-        gate = columns_of(proj, at["g"], self.heads * self.vdim) if self.gate else None
+        gate = columns_of(proj, at["g"], self.heads if self.gate == "sigmoid_head" else self.heads * self.vdim) if self.gate else None
         table, stride = b.table(run.group), b.table_stride(run.group)
-        if run.write_cache:
+        if self._prepares:
+            if not run.write_cache:
+                raise native.KernelError("masked attention: a layer that prepares its keys and values writes its own cache")
+            first = None
+            if self.value_mix is not None:
+                first = b.kept(("value_mix", self.kv_heads, self.vdim), proj.rows, self.kv_heads * self.vdim, torch.float32)
+            ptr = lambda t: t.data_ptr() if t is not None else None
+            b.launch("attention_masked", "mlr_qkv_prepare_cache", address(self.desc), proj.ptr, proj.ld, k.ptr, k.ld, v.ptr, v.ld, proj.is_bf16,
+                     ptr(self._biases[0]), ptr(self._biases[1]), ptr(self._biases[2]), int(self.unit_qk), int(self.unit_v), self.eps,
+                     first.ptr if first is not None else None, first.ld if first is not None else 0,
+                     {None: 0, "first": 1, "later": 2}[self.value_mix], self._lambda, run.cache.data_ptr(), run.cache.shape[0],
+                     b.meta("positions"), b.meta("segment_of_row"), table, stride, b.page_size, proj.rows, b.status, b.stream)
+        elif run.write_cache:
             b.launch("attention_masked", "mlr_kv_rope_cache", address(self.desc), k.ptr, k.ld, v.ptr, v.ld, proj.is_bf16,
                      run.cache.data_ptr(), run.cache.shape[0], b.meta("positions"), b.meta("segment_of_row"), table, stride,
                      b.page_size, proj.rows, b.status, b.stream)

@@ -57,15 +57,22 @@ class GatedBiasFeedForward(FeedForward):
     """Gated feed-forward whose three projections have biases: `down(act(gate x + b_g) * (up x + b_u)) + b_d`,
     act = SiLU or the tanh form of GELU.  Gate and up are one stacked product; a row-wise kernel adds their
     biases and gates; the last bias travels with the result (`Buf.bias`) to whoever adds it into the stream.
-    Parameters: hidden_size, intermediate_size, activation ("silu" | "gelu_tanh").  Weights: "gate", "up"
-    [I, width], "down" [width, I], "gate_bias", "up_bias" [I], "down_bias" [width]."""
-    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+    A third activation, "swish", is `g * sigmoid(alpha * g) * (u + up_offset)` with g = gate x + b_g and u = up x + b_u, after
+    g <- min(g, limit) and u <- clamp(u, -limit, limit) where a limit is given.
+    Parameters: hidden_size, intermediate_size, activation ("silu" | "gelu_tanh" | "swish"), and for "swish" alpha (default 1),
+    limit (default none), up_offset (default 0).  Weights: "gate", "up" [I, width], "down" [width, I], "gate_bias", "up_bias" [I],
+    "down_bias" [width]."""
+    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "swish": 2}
 
     def __init__(self, spec):
         super().__init__(spec)
         self.width = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
         self.activation = self.ACTIVATIONS[spec.params.get("activation", "silu")]
+        self.alpha, self.limit = float(spec.params.get("alpha", 1.0)), float(spec.params.get("limit") or 0.0)
+        self.up_offset = float(spec.params.get("up_offset", 0.0))
+        if self.activation != 2 and (self.alpha != 1.0 or self.limit or self.up_offset):
+            raise ValueError("alpha, limit and up_offset belong to the activation 'swish'")
         self.w_gate_up = self.w_down = self.b_gate = self.b_up = self.b_down = None
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -89,8 +96,8 @@ class GatedBiasFeedForward(FeedForward):
         rt = b.rt
         both = rt.linear(b, x, self.w_gate_up, activation=True)
         act = b.temp(x.rows, self.inter, rt.dtype)
-        b.launch("elementwise", "mlr_gated_bias", both.ptr, both.ld, self.b_gate.data_ptr(), self.b_up.data_ptr(), act.ptr, act.ld,
-                 act.is_bf16, x.rows, self.inter, self.activation, b.stream)
+        b.launch("elementwise", "mlr_gated_bias_shaped", both.ptr, both.ld, self.b_gate.data_ptr(), self.b_up.data_ptr(), act.ptr, act.ld,
+                 act.is_bf16, x.rows, self.inter, self.activation, self.alpha, self.limit, self.up_offset, b.stream)
         out = rt.linear(b, act, self.w_down, out_dtype=torch.float32)
         out.bias = self.b_down
         return out

@@ -133,3 +133,53 @@ class GroupRmsNorm(Norm):
 
 
 register_part("norm", "group_rmsnorm", GroupRmsNorm)
+
+
+class LayerNorm(Norm):
+    """Layer norm with weight and bias: `(x - mean) / sqrt(var + eps) * w + b`, the variance as the mean of the squared
+    deviations, all float32 (`mlr_depth_norm` of `layernorm.cu`, which a block may also hand the sub-layers' results
+    and the stream's earlier states: `parts/block.py`).  Parameters: width, eps.  Weights: "weight", "bias" [width]."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width = int(spec.params["width"])
+        self.eps = float(spec.params["eps"])
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.spec.weights["weight"], (self.width,), "vector", ("one_plus_normal", 0.01)),
+                WeightSpec(self.spec.weights["bias"], (self.width,), "vector", ("normal", 0.02))]
+
+    def kernel_modules(self, dtype) -> List[str]:
+        return ["layernorm"]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
+        self.weight = rt.vector(tensors[self.spec.weights["weight"]]).float().contiguous()
+        self.bias = rt.vector(tensors[self.spec.weights["bias"]]).float().contiguous()
+
+    def foldable(self):
+        """The block before may apply this norm in the launch that ends it and leave the result on the builder (`prepared`)."""
+        return ("layernorm", self)
+
+    def same_shape(self, other) -> bool:
+        return isinstance(other, LayerNorm) and other.width == self.width
+
+    def emit(self, b, h, delta, wanted_only: bool = False):
+        if delta is not None and (delta.slices or delta.norm is not None or delta.dtype is not torch.float32 or wanted_only):
+            raise native.KernelError("the layer norm adds a plain float32 [rows, width] contribution, for all rows only")
+        prepared, b.prepared = b.prepared, None
+        if (delta is None and not wanted_only and isinstance(prepared, dict) and prepared.get("layernorm") is self
+                and prepared.get("stream") is h):
+            return prepared["out"]          # the launch that ended the block before has applied this norm already
+        count = b.want if wanted_only else h.rows
+        out = b.temp(count, self.width, b.rt.dtype)
+        bias = getattr(delta, "bias", None) if delta is not None else None
+        b.launch("layernorm", "mlr_depth_norm", h.ptr, delta.ptr if delta is not None else None, delta.ld if delta is not None else 0,
+                 None, 0, bias.data_ptr() if bias is not None else None, None, 0, 0, None, self.weight.data_ptr(), self.bias.data_ptr(),
+                 self.eps, out.ptr, out.ld, out.is_bf16, b.meta("want_rows") if wanted_only else None, count, self.width,
+                 int(delta is not None), b.stream, need="want" if wanted_only else None)
+        return out
+
+
+register_part("norm", "layernorm", LayerNorm)

@@ -54,14 +54,17 @@ class RotaryFrequencies(PositionEncoding):
     """Rotation given as its frequencies only: `freq_i = base^(-2i/dims) / factor`, i < dims/2.  The kernels
     that use it compute `position * freq_i` and its cosine and sine in float32 themselves, so no table
     exists and no largest position: `factor` > 1 is linear position scaling.  Only the first `dims`
-    values of a head are rotated (value i with value i + dims/2); a mixer's heads may be wider.
-    Parameters: base, dims, factor (default 1).  No weights."""
+    values of a head are rotated; a mixer's heads may be wider.  Value i turns with value i + dims/2, or, with
+    `interleaved`, value 2i with value 2i + 1: (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = position * freq_i
+    (a mixer's kernels must know that layout; those that do not refuse it).
+    Parameters: base, dims, factor (default 1), interleaved (default False).  No weights."""
 
     def __init__(self, spec):
         super().__init__(spec)
         self.base = float(spec.params["base"])
         self.dims = int(spec.params["dims"])
         self.factor = float(spec.params.get("factor", 1.0))
+        self.interleaved = bool(spec.params.get("interleaved", False))
         if self.dims < 0 or self.dims % 2 or self.base <= 0 or self.factor <= 0:
             raise ValueError(f"a rotation of {self.dims} values with base {self.base} and factor {self.factor} is not defined")
         self._freq: Optional[torch.Tensor] = None
