@@ -322,7 +322,23 @@ def niridra_config(width, ff, heads, kv, dim, layers, chunk, vocab):
             "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": made}
 
 
-DESIGNS = {"gopevik": gopevik_config, "niridra": niridra_config}
+def sopetar_config(width, ff, heads, kv, dim, layers, chunk, vocab):
+    """Latent attention (a cached vector of 3/4 `dim` values and a rotated key part of 1/4 `dim` per token, a window of half the
+    context, learned sinks, a gate per head) in turn with grouped-query attention without rotation (biases, unit heads, capped
+    scores, a distance bias, the same window with four kept first tokens, values mixed with the first such layer's); every layer
+    with one layer norm, a clamped gated feed-forward with biases beside its mixer, and the average over all earlier states."""
+    window = max(chunk // 2, 1)
+    latent = {"heads": heads, "dim": dim, "rot_dim": dim // 4, "vdim": dim, "kv_rank": dim - dim // 4, "scale": (dim + dim // 4) ** -0.5,
+              "rot": {"base": 1e4, "dims": dim // 4}, "mask": {"size": window}}
+    attention = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0, "v_mix": True,
+                 "mask": {"size": window, "keep_first": 4}}
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    return {"architecture": "Sopetar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": [{"type": "attention", "mixer": attention, "mlp": mlp} if i % 2 else {"type": "latent_attention", "mixer": latent, "mlp": mlp}
+                       for i in range(layers)]}
+
+
+DESIGNS = {"gopevik": gopevik_config, "niridra": niridra_config, "sopetar": sopetar_config}
 
 
 def compare_designs(args) -> int:
