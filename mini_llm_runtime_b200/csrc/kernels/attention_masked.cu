@@ -23,6 +23,7 @@
 // decoded tokens, short portions and the float32 path; `mlr_attention_masked_tiles` (below) takes the
 // prompt portions of the bfloat16 path in tiles of 64 rows on the tensor cores.
 #include "common.cuh"
+#include <type_traits>
 
 struct MaskedAttentionSpec {
     const float* freq;     // [rot_dims / 2] float32 on the device, or null
@@ -455,6 +456,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// tanh for the capped scores of the tile kernel, without a branch: below 0.3 an odd polynomial (the first term left out is
+// 5e-8 of x), above it 1 - 2 / (e^(2|x|) + 1) from the special-function unit (absolute error about 2e-7); both are computed
+// and one is chosen.
+__device__ __forceinline__ float tile_tanh(float x) {
+    const float ax = fabsf(x), x2 = x * x;
+    const float poly = x * fmaf(x2, fmaf(x2, fmaf(x2, fmaf(x2, 62.0f / 2835.0f, -17.0f / 315.0f), 2.0f / 15.0f), -1.0f / 3.0f), 1.0f);
+    const float big = copysignf(1.0f - __fdividef(2.0f, __expf(2.0f * ax) + 1.0f), x);
+    return ax < 0.3f ? poly : big;
+}
+
+// What a product becomes in the tile kernel: `to_cap` = scale / softcap (or scale without a cap), `back` = key - position as a
+// float (exact: both are far below 2^24), so that the distance bias is one fused multiply-add.
+template <bool CAPPED>
+__device__ __forceinline__ float tile_score(float dot, float back, float to_cap, float cap, float slope) {
+    float v = dot * to_cap;
+    if (CAPPED) v = cap * tile_tanh(v);
+    return fmaf(slope, back, v);
+}
+
 __device__ __forceinline__ int first_visible(int position, const MaskedAttentionSpec& s) {
     int lo = 0;
     if (s.window > 0) lo = max(lo, position - s.window + 1);
@@ -489,7 +509,8 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
     const int keep_first = s.window > 0 ? s.keep_first : 0;
     const float slope = s.slopes ? s.slopes[head] : 0.0f;
     const float sink_score = s.sinks ? s.sinks[head] : 0.0f;
-    const bool plain_scores = !(s.softcap > 0.0f) && !s.slopes;
+    const bool capped = s.softcap > 0.0f, plain_scores = !capped && !s.slopes;
+    const float to_cap = capped ? s.scale / s.softcap : s.scale;
     if (threadIdx.x == 0) bad = 0;
 
     // The block's queries, rotated in float32, as bfloat16.
@@ -606,29 +627,35 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
                 tile_a = fmaxf(tile_a, fmaxf(S[nt][0], S[nt][1]));
                 tile_b = fmaxf(tile_b, fmaxf(S[nt][2], S[nt][3]));
             }
-        } else if (open) {
-#pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = kt + nt * 8 + 2 * t + (e & 1);
-                    const float v = mlr_masked_score(S[nt][e], (e < 2 ? pos_a : pos_b) - key, slope, s);
-                    S[nt][e] = v;
-                    if (e < 2) tile_a = fmaxf(tile_a, v); else tile_b = fmaxf(tile_b, v);
-                }
         } else {
+            // key - position of this thread's first key of the tile, for its two rows; the other keys lie a constant further.
+            const float back_a = static_cast<float>(kt + 2 * t - pos_a), back_b = static_cast<float>(kt + 2 * t - pos_b);
+            auto shape = [&](auto capped_tag, auto masked_tag) {
+                constexpr bool kCapped = decltype(capped_tag)::value, kMasked = decltype(masked_tag)::value;
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
+                for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = kt + nt * 8 + 2 * t + (e & 1);
-                    const bool upper = e < 2;
-                    const bool seen = upper ? (row_a && key <= pos_a && (key >= lo_a || key < keep_first))
-                                            : (row_b && key <= pos_b && (key >= lo_b || key < keep_first));
-                    const float v = seen ? mlr_masked_score(S[nt][e], (upper ? pos_a : pos_b) - key, slope, s) : -INFINITY;
-                    S[nt][e] = v;
-                    if (upper) tile_a = fmaxf(tile_a, v); else tile_b = fmaxf(tile_b, v);
-                }
+                    for (int e = 0; e < 4; ++e) {
+                        const bool upper = e < 2;
+                        const float further = static_cast<float>(nt * 8 + (e & 1));
+                        float v = tile_score<kCapped>(S[nt][e], (upper ? back_a : back_b) + further, to_cap, s.softcap, slope);
+                        if (kMasked) {
+                            const int key = kt + nt * 8 + 2 * t + (e & 1);
+                            const bool seen = upper ? (row_a && key <= pos_a && (key >= lo_a || key < keep_first))
+                                                    : (row_b && key <= pos_b && (key >= lo_b || key < keep_first));
+                            if (!seen) v = -INFINITY;
+                        }
+                        S[nt][e] = v;
+                        if (upper) tile_a = fmaxf(tile_a, v); else tile_b = fmaxf(tile_b, v);
+                    }
+            };
+            if (open) {
+                if (capped) shape(std::true_type{}, std::false_type{});
+                else shape(std::false_type{}, std::false_type{});
+            } else {
+                if (capped) shape(std::true_type{}, std::true_type{});
+                else shape(std::false_type{}, std::true_type{});
+            }
         }
         tile_a = fmaxf(tile_a, __shfl_xor_sync(0xffffffffu, tile_a, 1));
         tile_a = fmaxf(tile_a, __shfl_xor_sync(0xffffffffu, tile_a, 2));
@@ -706,6 +733,278 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
             *reinterpret_cast<__nv_bfloat162*>(out + row * ldo + col) = __floats2bfloat162_rn(v0 * s.out_scale, v1 * s.out_scale);
         }
     }
+}
+
+// ---- few rows per request in bfloat16 (decoded tokens, short portions): one block per (segment, kv head, range of keys) takes
+// ALL query heads that share the kv head, so the keys and values of a range are read once for the group.  The heads of the
+// group are the rows of the tensor-core tiles (up to 16; rows past the group are zeros): S = Q K^T by mma.sync, mask and
+// softmax in float32, the weights as two bfloat16 terms against the values, float32 sums, as in the tile kernel above.  A
+// tile of 64 keys is cut over the four warps (16 keys each, every warp with a running maximum and sums of its own); at the
+// end the warps' results are added up in shared memory and go to `partial` in the row kernel's layout (the same merge
+// kernel follows), or, when the block has seen every key of the row, straight to the output.
+template <int NV>
+__global__ void __launch_bounds__(128) attention_masked_group_kernel(const __nv_bfloat16* q, int ldq, const __nv_bfloat16* gate, int ld_gate,
+                                                                     __nv_bfloat16* out, int ldo, const __nv_bfloat16* cache, int num_pages,
+                                                                     const int* positions, const int* segment_of_row, const int* block_table,
+                                                                     int table_stride, int page_size, MaskedAttentionSpec s, const int* items,
+                                                                     const int* segment_info, int split_keys, int max_splits, float* partial,
+                                                                     int* status) {
+    mlr_grid_wait();
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int qstride = s.dim + kPad, vstride = s.shared_kv ? qstride : s.vdim + kPad;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem);
+    __nv_bfloat16* Ks = Qs + 16 * qstride;
+    __nv_bfloat16* Vs = s.shared_kv ? Ks : Ks + 2 * kKeys * qstride;        // two stages of each; values that are their keys' start are read there
+    float* merged = reinterpret_cast<float*>(Ks);                            // [4 warps][16 rows][vdim + 2], once the last tile is done
+    __shared__ int bad;
+
+    const int* info = segment_info + 4 * (items ? items[blockIdx.x] : blockIdx.x);
+    const int first_row = info[0], n_rows = min(info[1], kRowsPerItem);
+    const int kv_head = blockIdx.y, group = s.heads / s.kv_heads, head0 = kv_head * group;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const size_t page_elems = static_cast<size_t>(s.kv_heads) * page_size * (s.shared_kv ? s.dim : s.dim + s.vdim);
+    const size_t key_plane = s.shared_kv ? 0 : static_cast<size_t>(s.kv_heads) * page_size * s.dim;
+    const bool capped = s.softcap > 0.0f;
+    const float to_cap = capped ? s.scale / s.softcap : s.scale;
+    const float slope_a = (s.slopes && g < group) ? s.slopes[head0 + g] : 0.0f;
+    const float slope_b = (s.slopes && g + 8 < group) ? s.slopes[head0 + g + 8] : 0.0f;
+    const int ksteps = s.dim / 16, half = s.rot_dims / 2, mstride = s.vdim + 2;
+    const uint32_t qs_base = static_cast<uint32_t>(__cvta_generic_to_shared(Qs));
+    const uint32_t ks_base = static_cast<uint32_t>(__cvta_generic_to_shared(Ks));
+    const uint32_t vs_base = static_cast<uint32_t>(__cvta_generic_to_shared(Vs));
+    if (threadIdx.x == 0) bad = 0;
+
+    for (int j = 0; j < n_rows; ++j) {
+        __syncthreads();            // the row before is done with the shared memory
+        const int row = first_row + j;
+        const int position = positions[row];
+        const int* table = block_table + static_cast<size_t>(segment_of_row[row]) * table_stride;
+        const int lo = first_visible(position, s);
+        const int kept = (s.window > 0 && s.keep_first > 0) ? min(s.keep_first, lo) : 0;       // keys [0, kept) are seen beside [lo, position]
+        int tile_first = (lo / kKeys) * kKeys, tile_last = position;
+        if (partial) {
+            tile_first += blockIdx.z * split_keys;
+            tile_last = min(position, tile_first + split_keys - 1);
+            if (tile_first > position) continue;           // the merge reads only the ranges that exist for this row
+        }
+        // The group's queries, rotated in float32, as bfloat16.
+        for (int i = threadIdx.x; i < 16 * s.dim; i += 128) {
+            const int r = i / s.dim, c = i % s.dim;
+            float value = 0.0f;
+            if (r < group) {
+                const __nv_bfloat16* qrow = q + static_cast<size_t>(row) * ldq + static_cast<size_t>(head0 + r) * s.dim;
+                value = __bfloat162float(qrow[c]);
+                if (c < s.rot_dims) {
+                    float sn, cs;
+                    sincosf(static_cast<float>(position) * s.freq[c < half ? c : c - half], &sn, &cs);
+                    const float other = __bfloat162float(qrow[c < half ? c + half : c - half]);
+                    value = c < half ? value * cs - other * sn : value * cs + other * sn;
+                }
+            }
+            Qs[r * qstride + c] = __float2bfloat16_rn(value);
+        }
+        const int kept_tiles = (kept > 0 && (!partial || blockIdx.z == 0)) ? (kept + kKeys - 1) / kKeys : 0;
+        const int all_tiles = kept_tiles + (tile_last - tile_first) / kKeys + 1;
+        auto tile_start = [&](int i) { return i < kept_tiles ? i * kKeys : tile_first + (i - kept_tiles) * kKeys; };
+        // Keys (and values) of a tile go into one of two stages by asynchronous copies, two threads per key; keys the row does
+        // not see become zeros.
+        auto fetch = [&](int i, int into) {
+            const bool early = i < kept_tiles;
+            const int see_lo = early ? 0 : lo, see_hi = early ? kept - 1 : tile_last;
+            const int key = threadIdx.x >> 1, at = tile_start(i) + key;
+            bool real = at >= see_lo && at <= see_hi;
+            const __nv_bfloat16* ksrc = cache;
+            const __nv_bfloat16* vsrc = cache;
+            if (real) {
+                const int page = table[at / page_size];
+                if (page < 0 || page >= num_pages) {
+                    bad = 1;
+                    real = false;
+                } else {
+                    const size_t in_page = static_cast<size_t>(kv_head) * page_size + at % page_size;
+                    ksrc = cache + page * page_elems + in_page * s.dim;
+                    vsrc = cache + page * page_elems + key_plane + in_page * s.vdim;
+                }
+            }
+            __nv_bfloat16* krow = Ks + (into * kKeys + key) * qstride;
+            for (int c = (threadIdx.x & 1) * 8; c < s.dim; c += 16) mlr_async_copy16(krow + c, real ? ksrc + c : cache, real);
+            if (!s.shared_kv) {
+                __nv_bfloat16* vrow = Vs + (into * kKeys + key) * vstride;
+                for (int c = (threadIdx.x & 1) * 8; c < s.vdim; c += 16) mlr_async_copy16(vrow + c, real ? vsrc + c : cache, real);
+            }
+            mlr_async_commit();
+        };
+        float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
+        float O[NV][4];
+#pragma unroll
+        for (int nv = 0; nv < NV; ++nv) O[nv][0] = O[nv][1] = O[nv][2] = O[nv][3] = 0.0f;
+        fetch(0, 0);
+        int current = 0;
+        for (int ti = 0; ti < all_tiles; ++ti, current ^= 1) {
+            const bool early = ti < kept_tiles;
+            const int kt = tile_start(ti), see_lo = early ? 0 : lo, see_hi = early ? kept - 1 : tile_last;
+            mlr_async_wait();
+            __syncthreads();      // this tile has arrived (and Qs is written); no warp still reads the other stage
+            if (ti + 1 < all_tiles) fetch(ti + 1, current ^ 1);
+            const uint32_t kt_base = ks_base + static_cast<uint32_t>(current * kKeys * qstride * 2);
+            const uint32_t vt_base = vs_base + static_cast<uint32_t>(current * kKeys * vstride * 2);
+            float S[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.0f;
+            const uint32_t q_row = qs_base + static_cast<uint32_t>((((lane & 7) + ((lane >> 3) & 1) * 8) * qstride + (lane >> 4) * 8) * 2);
+            const uint32_t k_row = kt_base + static_cast<uint32_t>(((warp * 16 + (lane & 7)) * qstride + (lane >> 3) * 8) * 2);
+            for (int ks = 0; ks < ksteps; ks += 2) {
+                uint32_t a[4], a2[4] = {0, 0, 0, 0};
+                ldmatrix_x4(a, q_row + ks * 32);
+                const bool two = ks + 1 < ksteps;
+                if (two) ldmatrix_x4(a2, q_row + (ks + 1) * 32);
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    uint32_t kb[4];
+                    const uint32_t at = k_row + static_cast<uint32_t>((nt * 8 * qstride + ks * 16) * 2);
+                    if (two) {
+                        ldmatrix_x4(kb, at);
+                        mma_bf16(S[nt], a, kb[0], kb[1]);
+                        mma_bf16(S[nt], a2, kb[2], kb[3]);
+                    } else {
+                        ldmatrix_x2(kb, at);
+                        mma_bf16(S[nt], a, kb[0], kb[1]);
+                    }
+                }
+            }
+            // All rows of the block are heads at ONE position: a key is seen by all of them or by none.
+            const int key0 = kt + warp * 16 + 2 * t;
+            const float back = static_cast<float>(key0 - position);
+            float tile_a = -INFINITY, tile_b = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + nt * 8 + (e & 1);
+                    const float further = static_cast<float>(nt * 8 + (e & 1));
+                    float v = capped ? tile_score<true>(S[nt][e], back + further, to_cap, s.softcap, e < 2 ? slope_a : slope_b)
+                                     : tile_score<false>(S[nt][e], back + further, to_cap, 0.0f, e < 2 ? slope_a : slope_b);
+                    if (key < see_lo || key > see_hi) v = -INFINITY;
+                    S[nt][e] = v;
+                    if (e < 2) tile_a = fmaxf(tile_a, v); else tile_b = fmaxf(tile_b, v);
+                }
+            tile_a = fmaxf(tile_a, __shfl_xor_sync(0xffffffffu, tile_a, 1));
+            tile_a = fmaxf(tile_a, __shfl_xor_sync(0xffffffffu, tile_a, 2));
+            tile_b = fmaxf(tile_b, __shfl_xor_sync(0xffffffffu, tile_b, 1));
+            tile_b = fmaxf(tile_b, __shfl_xor_sync(0xffffffffu, tile_b, 2));
+            const float new_a = fmaxf(m_a, tile_a), new_b = fmaxf(m_b, tile_b);
+            const float alpha_a = (m_a == -INFINITY) ? 0.0f : __expf(m_a - new_a);
+            const float alpha_b = (m_b == -INFINITY) ? 0.0f : __expf(m_b - new_b);
+            m_a = new_a;
+            m_b = new_b;
+            l_a *= alpha_a;
+            l_b *= alpha_b;
+#pragma unroll
+            for (int nv = 0; nv < NV; ++nv) {
+                O[nv][0] *= alpha_a; O[nv][1] *= alpha_a; O[nv][2] *= alpha_b; O[nv][3] *= alpha_b;
+            }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float m = e < 2 ? new_a : new_b;
+                    const float p = S[nt][e] == -INFINITY ? 0.0f : __expf(S[nt][e] - m);
+                    S[nt][e] = p;
+                    if (e < 2) l_a += p; else l_b += p;
+                }
+            // O += P V over the warp's 16 keys, P as hi + lo
+            uint32_t hi[4], lo2[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float p0 = S[i >> 1][(i & 1) * 2], p1 = S[i >> 1][(i & 1) * 2 + 1];
+                const __nv_bfloat16 h0 = __float2bfloat16_rn(p0), h1 = __float2bfloat16_rn(p1);
+                hi[i] = pack_bf16(__bfloat162float(h0), __bfloat162float(h1));
+                lo2[i] = pack_bf16(p0 - __bfloat162float(h0), p1 - __bfloat162float(h1));
+            }
+            const uint32_t row_addr = vt_base + static_cast<uint32_t>(((warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * vstride + (lane >> 4) * 8) * 2);
+#pragma unroll
+            for (int nv = 0; nv < NV; nv += 2) {
+                if (nv * 8 < s.vdim) {          // the second tile of a pair may lie in the row's padding: it is computed and never stored
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, row_addr + nv * 16);
+                    mma_bf16(O[nv], hi, vb[0], vb[1]);
+                    mma_bf16(O[nv], lo2, vb[0], vb[1]);
+                    mma_bf16(O[nv + 1], hi, vb[2], vb[3]);
+                    mma_bf16(O[nv + 1], lo2, vb[2], vb[3]);
+                }
+            }
+        }
+        // The four warps' maxima, sums and weighted values side by side in shared memory, then added up head by head.
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+        __syncthreads();          // every warp is done with the tiles: their room becomes `merged`
+        {
+            float* mine_a = merged + (warp * 16 + g) * mstride;
+            float* mine_b = merged + (warp * 16 + g + 8) * mstride;
+            if (t == 0) {
+                mine_a[0] = m_a; mine_a[1] = l_a;
+                mine_b[0] = m_b; mine_b[1] = l_b;
+            }
+#pragma unroll
+            for (int nv = 0; nv < NV; ++nv) {
+                const int c = nv * 8 + 2 * t;
+                if (c < s.vdim) {
+                    mine_a[2 + c] = O[nv][0]; mine_a[2 + c + 1] = O[nv][1];
+                    mine_b[2 + c] = O[nv][2]; mine_b[2 + c + 1] = O[nv][3];
+                }
+            }
+        }
+        __syncthreads();
+        for (int r = 0; r < group; ++r) {
+            const int head = head0 + r;
+            float top = -INFINITY, w[4], sum = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) top = fmaxf(top, merged[(i * 16 + r) * mstride]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float m = merged[(i * 16 + r) * mstride];
+                w[i] = m == -INFINITY ? 0.0f : expf(m - top);
+                sum = fmaf(merged[(i * 16 + r) * mstride + 1], w[i], sum);
+            }
+            if (partial) {
+                float* mine = partial + ((static_cast<size_t>(blockIdx.x) * kRowsPerItem * s.kv_heads + j * s.heads + head) * max_splits +
+                                         blockIdx.z) * mstride;
+                if (threadIdx.x == 0) {
+                    mine[0] = top;
+                    mine[1] = sum;
+                }
+                for (int c = threadIdx.x; c < s.vdim; c += 128) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc = fmaf(merged[(i * 16 + r) * mstride + 2 + c], w[i], acc);
+                    mine[2 + c] = acc;
+                }
+            } else {
+                // The block saw every key of the row: the sink joins here, and the row is finished.
+                float scale_all = 1.0f;
+                if (s.sink) {
+                    const float sink_score = s.sinks ? s.sinks[head] : 0.0f;
+                    const float both = fmaxf(top, sink_score);
+                    scale_all = top == -INFINITY ? 0.0f : expf(top - both);
+                    sum = fmaf(sum, scale_all, expf(sink_score - both));
+                }
+                __nv_bfloat16* orow = out + static_cast<size_t>(row) * ldo + static_cast<size_t>(head) * s.vdim;
+                const __nv_bfloat16* grow = gate ? gate + static_cast<size_t>(row) * ld_gate + static_cast<size_t>(head) * (s.gate_kind == 3 ? 1 : s.vdim) : nullptr;
+                for (int c = threadIdx.x; c < s.vdim; c += 128) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc = fmaf(merged[(i * 16 + r) * mstride + 2 + c], w[i], acc);
+                    float value = sum > 0.0f ? acc * scale_all / sum : 0.0f;
+                    if (grow) value *= mlr_gate_value(__bfloat162float(grow[s.gate_kind == 3 ? 0 : c]), s.gate_kind);
+                    orow[c] = __float2bfloat16_rn(value * s.out_scale);
+                }
+            }
+        }
+    }
+    if (bad && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
+    mlr_grid_dependents_may_start();
 }
 
 int check_spec(const MaskedAttentionSpec* s, const char* who) {
@@ -808,6 +1107,34 @@ MLR_API int mlr_attention_masked(const MaskedAttentionSpec* spec, const void* q,
     const size_t shared = sizeof(float) * (spec->dim + kTile) + sizeof(long long) * kTile + 16;
     const dim3 grid(rows, spec->heads, max_splits);
     const dim3 merge_grid(rows, spec->heads);
+    const int group = spec->heads / spec->kv_heads;
+    if (act_bf16 && segment_info && group <= 16 && spec->dim % 16 == 0 && spec->dim <= 256 && spec->vdim % 8 == 0 && spec->vdim <= 128 &&
+        reinterpret_cast<uintptr_t>(cache) % 16 == 0) {
+        // Few rows per request in bfloat16: the query heads of a kv head share one block (and one reading of the keys).
+        const size_t stages = sizeof(__nv_bfloat16) * (static_cast<size_t>(16 + 2 * kKeys) * (spec->dim + kPad) +
+                                                       (spec->shared_kv ? 0 : 2 * kKeys * (spec->vdim + kPad)));
+        const size_t sums = sizeof(__nv_bfloat16) * 16 * (spec->dim + kPad) + sizeof(float) * 4 * 16 * (spec->vdim + 2);
+        const size_t group_shared = stages > sums ? stages : sums;
+        const dim3 group_grid(rows, spec->kv_heads, max_splits);
+#define MLR_GROUP(NV)                                                                                                                       \
+    do {                                                                                                                                    \
+        cudaFuncSetAttribute(attention_masked_group_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(group_shared)); \
+        mlr_launch((attention_masked_group_kernel<NV>), dim3(group_grid), dim3(128), group_shared, stream,                                  \
+                   static_cast<const __nv_bfloat16*>(q), ldq, static_cast<const __nv_bfloat16*>(gate), ld_gate,                              \
+                   static_cast<__nv_bfloat16*>(out), ldo, static_cast<const __nv_bfloat16*>(cache), num_pages, positions, segment_of_row,    \
+                   block_table, table_stride, page_size, *spec, items, segment_info, split_keys, max_splits, partial, status);              \
+    } while (0)
+        if (spec->vdim <= 32) MLR_GROUP(4);
+        else if (spec->vdim <= 64) MLR_GROUP(8);
+        else if (spec->vdim <= 96) MLR_GROUP(12);
+        else MLR_GROUP(16);
+#undef MLR_GROUP
+        if (partial)
+            mlr_launch((attention_masked_merge_kernel<__nv_bfloat16, 2>), dim3(merge_grid), dim3(kThreads), 0, stream, partial,
+                       static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__nv_bfloat16*>(out), ldo, positions, *spec, items,
+                       segment_info, split_keys, max_splits);
+        return mlr_launched("attention_masked");
+    }
 #define MLR_ROWS(T, DPT)                                                                                                                    \
     do {                                                                                                                                    \
         mlr_launch((attention_masked_kernel<T, DPT>), dim3(grid), dim3(kThreads), shared, stream, static_cast<const T*>(q), ldq,            \
