@@ -20,8 +20,9 @@
 // of 64 with a running maximum, one block per (row, query head), so a row's result depends on its
 // position and on the cache only.  Scores, weights and sums are float32; q, the cache, the gate and
 // the output are float32 or bfloat16.  Keys that are not visible are never loaded.  That kernel serves
-// decoded tokens, short portions and the float32 path; `mlr_attention_masked_tiles` (below) takes the
-// prompt portions of the bfloat16 path in tiles of 64 rows on the tensor cores.
+// the float32 path and sizes the others do not take.  In bfloat16, decoded tokens and short portions go to a kernel whose
+// block holds all query heads of ONE kv head (the heads are the rows of its tensor-core tiles, so a range of keys is read
+// once for the group), and `mlr_attention_masked_tiles` (below) takes the prompt portions in tiles of 64 rows.
 #include "common.cuh"
 #include <type_traits>
 
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(kThreads) kv_rope_cache_kernel(const T* k, int
     mlr_grid_dependents_may_start();
 }
 
-// The step's q, k and v as the projection left them, made ready for attention, one block per row and one warp per head:
+// The step's q, k and v as the projection left them, made ready for attention, blocks of four warps per row and one warp per head:
 //   q_h <- (q_h + bias) / rms(q_h)          in place         (biases and the division only where asked for)
 //   k_g <- (k_g + bias) / rms(k_g), rotated like `kv_rope_cache_kernel` does, into the cache
 //   v_g <- (v_g + bias) / rms(v_g);  mix 1: first[row] = v;  mix 2: v <- (1 - lambda) v + lambda first[row];  into the cache
@@ -125,7 +126,7 @@ __global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int l
                static_cast<size_t>(position % page_size) * s.vdim;
     const int half = s.rot_dims / 2;
     const float p = static_cast<float>(position);
-    for (int unit = warp; unit < s.heads + 2 * s.kv_heads; unit += kThreads / 32) {
+    for (int unit = blockIdx.y * (kThreads / 32) + warp; unit < s.heads + 2 * s.kv_heads; unit += gridDim.y * (kThreads / 32)) {
         const int kind = unit < s.heads ? 0 : (unit < s.heads + s.kv_heads ? 1 : 2);
         const int head = kind == 0 ? unit : (kind == 1 ? unit - s.heads : unit - s.heads - s.kv_heads);
         const int n = kind == 2 ? s.vdim : s.dim;
@@ -512,6 +513,7 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
     const bool capped = s.softcap > 0.0f, plain_scores = !capped && !s.slopes;
     const float to_cap = capped ? s.scale / s.softcap : s.scale;
     if (threadIdx.x == 0) bad = 0;
+    __syncthreads();
 
     // The block's queries, rotated in float32, as bfloat16.
     const int half = s.rot_dims / 2;
@@ -547,17 +549,22 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
 
     // Keys and values of a tile of 64 positions go from their pages into one of two stages by asynchronous copies, so
     // that the next tile arrives while this one is multiplied; rows no query of the block may see become zeros.
-    auto fetch = [&](int kt, int into) {
+    // The page of this thread's key of the tile at `kt` (0 where no query of the block sees the key).  It is read one tile
+    // before the copies that need it are issued, so that no warp waits for the table between two tiles.
+    auto page_for = [&](int kt) {
+        const int position = kt + (threadIdx.x >> 1);
+        const bool real = position <= last_pos && (position >= lo_min || position < keep_first);
+        return real ? __ldg(table + position / page_size) : 0;
+    };
+    auto fetch = [&](int kt, int into, int page) {
         __nv_bfloat16* kdst = Ks + into * kKeys * qstride;
         __nv_bfloat16* vdst = Vs + into * kKeys * vstride;
-        // Two threads per key: the page and the row's addresses once, then every other 16-byte piece of the key's row
-        // and of its value row.
+        // Two threads per key: the row's addresses once, then every other 16-byte piece of the key's row and of its value row.
         const int key = threadIdx.x >> 1, position = kt + key;
         bool real = position <= last_pos && (position >= lo_min || position < keep_first);
         const __nv_bfloat16* ksrc = cache;
         const __nv_bfloat16* vsrc = cache;
         if (real) {
-            const int page = table[position / page_size];
             if (page < 0 || page >= num_pages) {
                 bad = 1;
                 real = false;
@@ -579,13 +586,17 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
     const int early_tiles = (min(keep_first, kt_first) + kKeys - 1) / kKeys;
     const int all_tiles = early_tiles + (last_pos - kt_first) / kKeys + 1;
     auto tile_start = [&](int i) { return i < early_tiles ? i * kKeys : kt_first + (i - early_tiles) * kKeys; };
-    fetch(tile_start(0), 0);
+    fetch(tile_start(0), 0, page_for(tile_start(0)));
+    int page_ahead = all_tiles > 1 ? page_for(tile_start(1)) : 0;
     int current = 0;
     for (int ti = 0; ti < all_tiles; ++ti, current ^= 1) {
         const int kt = tile_start(ti);
         mlr_async_wait();
         __syncthreads();      // this tile has arrived (and Qs is written); no warp still reads the other stage
-        if (ti + 1 < all_tiles) fetch(tile_start(ti + 1), current ^ 1);
+        if (ti + 1 < all_tiles) {
+            fetch(tile_start(ti + 1), current ^ 1, page_ahead);
+            if (ti + 2 < all_tiles) page_ahead = page_for(tile_start(ti + 2));
+        }
         const uint32_t kt_base = ks_base + static_cast<uint32_t>(current * kKeys * qstride * 2);
         const uint32_t vt_base = vs_base + static_cast<uint32_t>(current * kKeys * vstride * 2);
         float S[8][4];
@@ -787,28 +798,17 @@ __global__ void __launch_bounds__(128) attention_masked_group_kernel(const __nv_
             tile_last = min(position, tile_first + split_keys - 1);
             if (tile_first > position) continue;           // the merge reads only the ranges that exist for this row
         }
-        // The group's queries, rotated in float32, as bfloat16.
-        for (int i = threadIdx.x; i < 16 * s.dim; i += 128) {
-            const int r = i / s.dim, c = i % s.dim;
-            float value = 0.0f;
-            if (r < group) {
-                const __nv_bfloat16* qrow = q + static_cast<size_t>(row) * ldq + static_cast<size_t>(head0 + r) * s.dim;
-                value = __bfloat162float(qrow[c]);
-                if (c < s.rot_dims) {
-                    float sn, cs;
-                    sincosf(static_cast<float>(position) * s.freq[c < half ? c : c - half], &sn, &cs);
-                    const float other = __bfloat162float(qrow[c < half ? c + half : c - half]);
-                    value = c < half ? value * cs - other * sn : value * cs + other * sn;
-                }
-            }
-            Qs[r * qstride + c] = __float2bfloat16_rn(value);
-        }
         const int kept_tiles = (kept > 0 && (!partial || blockIdx.z == 0)) ? (kept + kKeys - 1) / kKeys : 0;
         const int all_tiles = kept_tiles + (tile_last - tile_first) / kKeys + 1;
         auto tile_start = [&](int i) { return i < kept_tiles ? i * kKeys : tile_first + (i - kept_tiles) * kKeys; };
         // Keys (and values) of a tile go into one of two stages by asynchronous copies, two threads per key; keys the row does
         // not see become zeros.
-        auto fetch = [&](int i, int into) {
+        auto page_for = [&](int i) {      // read one tile before `fetch` needs it; 0 for a key the row does not see
+            const bool early = i < kept_tiles;
+            const int at = tile_start(i) + (threadIdx.x >> 1);
+            return (at >= (early ? 0 : lo) && at <= (early ? kept - 1 : tile_last)) ? __ldg(table + at / page_size) : 0;
+        };
+        auto fetch = [&](int i, int into, int page) {
             const bool early = i < kept_tiles;
             const int see_lo = early ? 0 : lo, see_hi = early ? kept - 1 : tile_last;
             const int key = threadIdx.x >> 1, at = tile_start(i) + key;
@@ -816,7 +816,6 @@ __global__ void __launch_bounds__(128) attention_masked_group_kernel(const __nv_
             const __nv_bfloat16* ksrc = cache;
             const __nv_bfloat16* vsrc = cache;
             if (real) {
-                const int page = table[at / page_size];
                 if (page < 0 || page >= num_pages) {
                     bad = 1;
                     real = false;
@@ -834,18 +833,39 @@ __global__ void __launch_bounds__(128) attention_masked_group_kernel(const __nv_
             }
             mlr_async_commit();
         };
+        // The first tile's copies are on their way while the queries are made ready.
+        fetch(0, 0, page_for(0));
+        int page_ahead = all_tiles > 1 ? page_for(1) : 0;
+        // The group's queries, rotated in float32, as bfloat16.
+        for (int i = threadIdx.x; i < 16 * s.dim; i += 128) {
+            const int r = i / s.dim, c = i % s.dim;
+            float value = 0.0f;
+            if (r < group) {
+                const __nv_bfloat16* qrow = q + static_cast<size_t>(row) * ldq + static_cast<size_t>(head0 + r) * s.dim;
+                value = __bfloat162float(qrow[c]);
+                if (c < s.rot_dims) {
+                    float sn, cs;
+                    sincosf(static_cast<float>(position) * s.freq[c < half ? c : c - half], &sn, &cs);
+                    const float other = __bfloat162float(qrow[c < half ? c + half : c - half]);
+                    value = c < half ? value * cs - other * sn : value * cs + other * sn;
+                }
+            }
+            Qs[r * qstride + c] = __float2bfloat16_rn(value);
+        }
         float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
         float O[NV][4];
 #pragma unroll
         for (int nv = 0; nv < NV; ++nv) O[nv][0] = O[nv][1] = O[nv][2] = O[nv][3] = 0.0f;
-        fetch(0, 0);
         int current = 0;
         for (int ti = 0; ti < all_tiles; ++ti, current ^= 1) {
             const bool early = ti < kept_tiles;
             const int kt = tile_start(ti), see_lo = early ? 0 : lo, see_hi = early ? kept - 1 : tile_last;
             mlr_async_wait();
             __syncthreads();      // this tile has arrived (and Qs is written); no warp still reads the other stage
-            if (ti + 1 < all_tiles) fetch(ti + 1, current ^ 1);
+            if (ti + 1 < all_tiles) {
+                fetch(ti + 1, current ^ 1, page_ahead);
+                if (ti + 2 < all_tiles) page_ahead = page_for(ti + 2);
+            }
             const uint32_t kt_base = ks_base + static_cast<uint32_t>(current * kKeys * qstride * 2);
             const uint32_t vt_base = vs_base + static_cast<uint32_t>(current * kKeys * vstride * 2);
             float S[2][4];
@@ -1057,13 +1077,16 @@ MLR_API int mlr_qkv_prepare_cache(const MaskedAttentionSpec* spec, void* q, int 
     MLR_REQUIRE(mix >= 0 && mix <= 2 && (mix == 0 || (first && ld_first >= spec->kv_heads * spec->vdim)), "qkv_prepare_cache: mixing needs the first values' buffer");
     if (rows == 0) return 0;
     const size_t shared = sizeof(float) * (kThreads / 32) * static_cast<size_t>(spec->dim > spec->vdim ? spec->dim : spec->vdim);
+    // Every warp takes one head of q, k or v where the grid may be that large; more heads than that are walked in turn.
+    const int units = spec->heads + 2 * spec->kv_heads, warps = kThreads / 32;
+    const dim3 grid(rows, (units + warps - 1) / warps < 64 ? (units + warps - 1) / warps : 64);
     if (act_bf16)
-        mlr_launch((qkv_prepare_cache_kernel<__nv_bfloat16>), dim3(rows), dim3(kThreads), shared, stream, static_cast<__nv_bfloat16*>(q), ldq,
+        mlr_launch((qkv_prepare_cache_kernel<__nv_bfloat16>), dim3(grid), dim3(kThreads), shared, stream, static_cast<__nv_bfloat16*>(q), ldq,
                    static_cast<const __nv_bfloat16*>(k), ld_k, static_cast<const __nv_bfloat16*>(v), ld_v, bq, bk, bv, unit_qk, unit_v, eps, first,
                    ld_first, mix, lambda, static_cast<__nv_bfloat16*>(cache), num_pages, positions, segment_of_row, block_table, table_stride,
                    page_size, *spec, status);
     else
-        mlr_launch((qkv_prepare_cache_kernel<float>), dim3(rows), dim3(kThreads), shared, stream, static_cast<float*>(q), ldq,
+        mlr_launch((qkv_prepare_cache_kernel<float>), dim3(grid), dim3(kThreads), shared, stream, static_cast<float*>(q), ldq,
                    static_cast<const float*>(k), ld_k, static_cast<const float*>(v), ld_v, bq, bk, bv, unit_qk, unit_v, eps, first, ld_first, mix,
                    lambda, static_cast<float*>(cache), num_pages, positions, segment_of_row, block_table, table_stride, page_size, *spec, status);
     return mlr_launched("qkv_prepare_cache");

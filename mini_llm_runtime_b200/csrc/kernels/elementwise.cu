@@ -672,12 +672,17 @@ __global__ void gated_bias_vec8_kernel(const T* gate_up, int ld, const float* bi
         float g[8], u[8], o[8];
         mlr_load8(gate_up + r * ld + c, g);
         mlr_load8(gate_up + r * ld + inter + c, u);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const float z = g[e] + (bias_gate ? bias_gate[c + e] : 0.0f);
-            const float up = u[e] + (bias_up ? bias_up[c + e] : 0.0f);
-            o[e] = gated_value(z, up, activation, shape);
+        // the biases of the eight columns as two 16-byte loads each
+        if (bias_gate) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(bias_gate + c)), b = __ldg(reinterpret_cast<const float4*>(bias_gate + c + 4));
+            g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
         }
+        if (bias_up) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(bias_up + c)), b = __ldg(reinterpret_cast<const float4*>(bias_up + c + 4));
+            u[0] += a.x; u[1] += a.y; u[2] += a.z; u[3] += a.w; u[4] += b.x; u[5] += b.y; u[6] += b.z; u[7] += b.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = gated_value(g[e], u[e], activation, shape);
         mlr_store8(out + r * ld_out + c, o);
     }
     mlr_grid_dependents_may_start();
@@ -694,7 +699,8 @@ MLR_API int mlr_gated_bias_shaped(const void* gate_up, int ld, const float* bias
     if (rows == 0) return 0;
     const int unit = act_bf16 ? 8 : 4;          // values in 16 bytes
     if (inter % 8 == 0 && ld % unit == 0 && ld_out % unit == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 &&
-        reinterpret_cast<uintptr_t>(out) % 16 == 0 && rows <= 65535) {
+        reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(bias_gate) % 16 == 0 &&
+        reinterpret_cast<uintptr_t>(bias_up) % 16 == 0 && rows <= 65535) {
         const dim3 grid((inter / 8 + 127) / 128, rows);
         if (act_bf16)
             mlr_launch((gated_bias_vec8_kernel<__nv_bfloat16>), dim3(grid), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(gate_up),
