@@ -490,14 +490,16 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
                                                                     int table_stride, int page_size, MaskedAttentionSpec s, int* status) {
     mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
-    const int qstride = s.dim + kPad, vstride = s.vdim + kPad;
+    const int qstride = s.dim + kPad, vstride = s.shared_kv ? qstride : s.vdim + kPad;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem);
     __nv_bfloat16* Ks = Qs + kRows * qstride;
-    __nv_bfloat16* Vs = Ks + 2 * kKeys * qstride;        // two stages of each
+    __nv_bfloat16* Vs = s.shared_kv ? Ks : Ks + 2 * kKeys * qstride;        // two stages of each; values that are their keys' start are read there
     __shared__ int bad;
 
+    // The list's last tiles first: in a long prompt they see the most keys, and the blocks that start last should be short.
+    const int tile_index = gridDim.y - 1 - blockIdx.y;
     const int head = blockIdx.x, kv_head = head / (s.heads / s.kv_heads);
-    const int segment = tiles[2 * blockIdx.y], tile_token = tiles[2 * blockIdx.y + 1];
+    const int segment = tiles[2 * tile_index], tile_token = tiles[2 * tile_index + 1];
     const int first = segment_info[4 * segment], count = segment_info[4 * segment + 1], start = segment_info[4 * segment + 2];
     const int n_rows = min(kRows, count - tile_token);
     const int first_pos = start + tile_token, last_pos = first_pos + n_rows - 1;
@@ -577,7 +579,8 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
         __nv_bfloat16* krow = kdst + key * qstride;
         __nv_bfloat16* vrow = vdst + key * vstride;
         for (int c = (threadIdx.x & 1) * 8; c < s.dim; c += 16) mlr_async_copy16(krow + c, real ? ksrc + c : cache, real);
-        for (int c = (threadIdx.x & 1) * 8; c < s.vdim; c += 16) mlr_async_copy16(vrow + c, real ? vsrc + c : cache, real);
+        if (!s.shared_kv)
+            for (int c = (threadIdx.x & 1) * 8; c < s.vdim; c += 16) mlr_async_copy16(vrow + c, real ? vsrc + c : cache, real);
         mlr_async_commit();
     };
     // Tiles of keys in the order they are walked: those of the kept first tokens that lie before the window's first tile, then
@@ -1077,9 +1080,11 @@ MLR_API int mlr_qkv_prepare_cache(const MaskedAttentionSpec* spec, void* q, int 
     MLR_REQUIRE(mix >= 0 && mix <= 2 && (mix == 0 || (first && ld_first >= spec->kv_heads * spec->vdim)), "qkv_prepare_cache: mixing needs the first values' buffer");
     if (rows == 0) return 0;
     const size_t shared = sizeof(float) * (kThreads / 32) * static_cast<size_t>(spec->dim > spec->vdim ? spec->dim : spec->vdim);
-    // Every warp takes one head of q, k or v where the grid may be that large; more heads than that are walked in turn.
+    // With few rows (decoded tokens) every warp takes one head of q, k or v; with many, a block of four warps walks its row's
+    // heads in turn, which the same number of blocks in flight does a little faster.
     const int units = spec->heads + 2 * spec->kv_heads, warps = kThreads / 32;
-    const dim3 grid(rows, (units + warps - 1) / warps < 64 ? (units + warps - 1) / warps : 64);
+    const int wanted = rows >= 592 ? 1 : (592 + rows - 1) / rows, most = (units + warps - 1) / warps;
+    const dim3 grid(rows, wanted < most ? wanted : most);
     if (act_bf16)
         mlr_launch((qkv_prepare_cache_kernel<__nv_bfloat16>), dim3(grid), dim3(kThreads), shared, stream, static_cast<__nv_bfloat16*>(q), ldq,
                    static_cast<const __nv_bfloat16*>(k), ld_k, static_cast<const __nv_bfloat16*>(v), ld_v, bq, bk, bv, unit_qk, unit_v, eps, first,
@@ -1201,7 +1206,8 @@ MLR_API int mlr_attention_masked_tiles(const MaskedAttentionSpec* spec, const vo
     MLR_REQUIRE((spec->gate_kind == 0) == (gate == nullptr), "attention_masked_tiles: the description and the call disagree about a gate");
     MLR_REQUIRE(reinterpret_cast<uintptr_t>(cache) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0, "attention_masked_tiles: alignment");
     if (n_tiles == 0) return 0;
-    const size_t shared = sizeof(__nv_bfloat16) * (static_cast<size_t>(kRows + 2 * kKeys) * (spec->dim + kPad) + 2 * kKeys * (spec->vdim + kPad));
+    const size_t shared = sizeof(__nv_bfloat16) * (static_cast<size_t>(kRows + 2 * kKeys) * (spec->dim + kPad) +
+                                                   (spec->shared_kv ? 0 : 2 * kKeys * (spec->vdim + kPad)));
     const dim3 grid(spec->heads, n_tiles);
 #define MLR_TILES(NV)                                                                                                              \
     do {                                                                                                                           \
