@@ -330,7 +330,7 @@ def sopetar_config(width, ff, heads, kv, dim, layers, chunk, vocab):
     window = max(chunk // 2, 1)
     latent = {"heads": heads, "dim": dim, "rot_dim": dim // 4, "vdim": dim, "kv_rank": dim - dim // 4, "scale": (dim + dim // 4) ** -0.5,
               "rot": {"base": 1e4, "dims": dim // 4}, "mask": {"size": window}}
-    attention = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0, "v_mix": True,
+    attention = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0, "v_mix": True,
                  "mask": {"size": window, "keep_first": 4}}
     mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
     return {"architecture": "Sopetar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},

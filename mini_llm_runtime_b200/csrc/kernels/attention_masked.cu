@@ -58,6 +58,13 @@ constexpr int kThreads = 128;
 constexpr int kMaxDimsPerThread = 8;  // vdim <= 1024; the kernels are built for 2 (vdim <= 256), 4 and 8 value columns a thread
 constexpr int kRowsPerItem = 16;      // a segment that the planner gives the row kernel brings at most this many rows
 
+// How many (row, head) results of one few-row segment the ranges' scratch holds: segments bring at most 16 / (heads per kv
+// head) rows, or ONE row where more than 16 heads share a kv head.
+__device__ __forceinline__ int partial_slots(const MaskedAttentionSpec& s) {
+    return max(kRowsPerItem * s.kv_heads, ((s.heads + kRowsPerItem - 1) / kRowsPerItem) * kRowsPerItem);
+}
+
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads) kv_rope_cache_kernel(const T* k, int ld_k, const T* v, int ld_v, T* cache, int num_pages,
                                                                  const int* positions, const int* segment_of_row,
@@ -351,7 +358,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
     }
     if (bad && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
     if (partial) {
-        float* mine = partial + ((static_cast<size_t>(blockIdx.x) * kRowsPerItem * s.kv_heads + j * s.heads + head) * max_splits +
+        float* mine = partial + ((static_cast<size_t>(blockIdx.x) * partial_slots(s) + j * s.heads + head) * max_splits +
                                  blockIdx.z) * (s.vdim + 2);
         if (threadIdx.x == 0) {
             mine[0] = running_max;
@@ -395,7 +402,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_merge_kernel(const 
     if (s.window > 0) lo = max(lo, position - s.window + 1);
     if (s.chunk > 0) lo = max(lo, (position / s.chunk) * s.chunk);
     const int splits = (position - (lo / kTile) * kTile) / split_keys + 1;
-    const float* mine = partial + (static_cast<size_t>(item) * kRowsPerItem * s.kv_heads + j * s.heads + head) * max_splits * (s.vdim + 2);
+    const float* mine = partial + (static_cast<size_t>(item) * partial_slots(s) + j * s.heads + head) * max_splits * (s.vdim + 2);
     const float sink_score = s.sinks ? s.sinks[head] : 0.0f;
     float top = s.sink ? sink_score : -INFINITY;
     for (int i = 0; i < splits; ++i) top = fmaxf(top, __ldcg(mine + static_cast<size_t>(i) * (s.vdim + 2)));
@@ -457,22 +464,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// tanh for the capped scores of the tile kernel, without a branch: below 0.3 an odd polynomial (the first term left out is
-// 5e-8 of x), above it 1 - 2 / (e^(2|x|) + 1) from the special-function unit (absolute error about 2e-7); both are computed
-// and one is chosen.
-__device__ __forceinline__ float tile_tanh(float x) {
-    const float ax = fabsf(x), x2 = x * x;
-    const float poly = x * fmaf(x2, fmaf(x2, fmaf(x2, fmaf(x2, 62.0f / 2835.0f, -17.0f / 315.0f), 2.0f / 15.0f), -1.0f / 3.0f), 1.0f);
-    const float big = copysignf(1.0f - __fdividef(2.0f, __expf(2.0f * ax) + 1.0f), x);
-    return ax < 0.3f ? poly : big;
-}
-
-// What a product becomes in the tile kernel: `to_cap` = scale / softcap (or scale without a cap), `back` = key - position as a
-// float (exact: both are far below 2^24), so that the distance bias is one fused multiply-add.
+// What a product becomes in the tensor-core kernels.  Without a cap `to_cap` = scale.  With one, `to_cap` = 2 log2(e) scale / cap
+// and cap * tanh(x) = cap - 2 cap / (e^(2x) + 1), one exponential and one reciprocal of the special-function unit for either
+// sign of x (e^(2x) = inf gives cap, 0 gives -cap).  Near x = 0 the difference loses relative precision, not absolute: the
+// score is off by a few 2^-23 of the cap, far below what bfloat16 queries and keys leave.  `back` = key - position as a float
+// (exact: both are far below 2^24), so that the distance bias is one fused multiply-add.
 template <bool CAPPED>
 __device__ __forceinline__ float tile_score(float dot, float back, float to_cap, float cap, float slope) {
     float v = dot * to_cap;
-    if (CAPPED) v = cap * tile_tanh(v);
+    if (CAPPED) {
+        float e, r;
+        asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(v));
+        asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(e + 1.0f));
+        v = fmaf(-2.0f * cap, r, cap);
+    }
     return fmaf(slope, back, v);
 }
 
@@ -496,8 +501,7 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
     __nv_bfloat16* Vs = s.shared_kv ? Ks : Ks + 2 * kKeys * qstride;        // two stages of each; values that are their keys' start are read there
     __shared__ int bad;
 
-    // The list's last tiles first: in a long prompt they see the most keys, and the blocks that start last should be short.
-    const int tile_index = gridDim.y - 1 - blockIdx.y;
+    const int tile_index = blockIdx.y;       // the planner lists the tiles that see the most keys first
     const int head = blockIdx.x, kv_head = head / (s.heads / s.kv_heads);
     const int segment = tiles[2 * tile_index], tile_token = tiles[2 * tile_index + 1];
     const int first = segment_info[4 * segment], count = segment_info[4 * segment + 1], start = segment_info[4 * segment + 2];
@@ -513,7 +517,7 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
     const float slope = s.slopes ? s.slopes[head] : 0.0f;
     const float sink_score = s.sinks ? s.sinks[head] : 0.0f;
     const bool capped = s.softcap > 0.0f, plain_scores = !capped && !s.slopes;
-    const float to_cap = capped ? s.scale / s.softcap : s.scale;
+    const float to_cap = capped ? 2.0f * 1.4426950408889634f * s.scale / s.softcap : s.scale;
     if (threadIdx.x == 0) bad = 0;
     __syncthreads();
 
@@ -774,12 +778,15 @@ __global__ void __launch_bounds__(128) attention_masked_group_kernel(const __nv_
 
     const int* info = segment_info + 4 * (items ? items[blockIdx.x] : blockIdx.x);
     const int first_row = info[0], n_rows = min(info[1], kRowsPerItem);
-    const int kv_head = blockIdx.y, group = s.heads / s.kv_heads, head0 = kv_head * group;
+    // More than 16 heads on a kv head: blocks of their own take them 16 at a time (`group`: this block's heads).
+    const int sharing = s.heads / s.kv_heads, chunks = (sharing + 15) / 16;
+    const int kv_head = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+    const int head0 = kv_head * sharing + chunk * 16, group = min(16, sharing - chunk * 16);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const size_t page_elems = static_cast<size_t>(s.kv_heads) * page_size * (s.shared_kv ? s.dim : s.dim + s.vdim);
     const size_t key_plane = s.shared_kv ? 0 : static_cast<size_t>(s.kv_heads) * page_size * s.dim;
     const bool capped = s.softcap > 0.0f;
-    const float to_cap = capped ? s.scale / s.softcap : s.scale;
+    const float to_cap = capped ? 2.0f * 1.4426950408889634f * s.scale / s.softcap : s.scale;
     const float slope_a = (s.slopes && g < group) ? s.slopes[head0 + g] : 0.0f;
     const float slope_b = (s.slopes && g + 8 < group) ? s.slopes[head0 + g + 8] : 0.0f;
     const int ksteps = s.dim / 16, half = s.rot_dims / 2, mstride = s.vdim + 2;
@@ -992,7 +999,7 @@ __global__ void __launch_bounds__(128) attention_masked_group_kernel(const __nv_
                 sum = fmaf(merged[(i * 16 + r) * mstride + 1], w[i], sum);
             }
             if (partial) {
-                float* mine = partial + ((static_cast<size_t>(blockIdx.x) * kRowsPerItem * s.kv_heads + j * s.heads + head) * max_splits +
+                float* mine = partial + ((static_cast<size_t>(blockIdx.x) * partial_slots(s) + j * s.heads + head) * max_splits +
                                          blockIdx.z) * mstride;
                 if (threadIdx.x == 0) {
                     mine[0] = top;
@@ -1104,8 +1111,8 @@ MLR_API int mlr_attention_masked(const MaskedAttentionSpec* spec, const void* q,
                                  int finer, float* partial, int* status, cudaStream_t stream) {
     // With `segment_info` the kernel runs over `n_items` segments of at most 16 rows each (`items` lists them; null: the
     // step's first n_items segments) and `rows` is not used; without it, over all `rows` rows.  With `partial` (float32,
-    // n_items * 16 * kv_heads * max_splits * (vdim + 2), segments of at most 16 / (heads / kv_heads) rows) and more than
-    // one split, every row's keys are cut into ranges of `split_keys` that run as blocks of their own, and a second
+    // n_items * max(16 * kv_heads, heads rounded up to 16) * max_splits * (vdim + 2); segments of at most 16 / (heads / kv_heads)
+    // rows, of one row where more than 16 heads share a kv head) and more than one split, every row's keys are cut into ranges of `split_keys` that run as blocks of their own, and a second
     // kernel adds the ranges up.
     if (check_spec(spec, "attention_masked")) return 1;
     if (segment_info) rows = n_items;          // a block per segment; it walks the segment's rows
@@ -1136,14 +1143,14 @@ MLR_API int mlr_attention_masked(const MaskedAttentionSpec* spec, const void* q,
     const dim3 grid(rows, spec->heads, max_splits);
     const dim3 merge_grid(rows, spec->heads);
     const int group = spec->heads / spec->kv_heads;
-    if (act_bf16 && segment_info && group <= 16 && spec->dim % 16 == 0 && spec->dim <= 256 && spec->vdim % 8 == 0 && spec->vdim <= 128 &&
+    if (act_bf16 && segment_info && spec->dim % 16 == 0 && spec->dim <= 256 && spec->vdim % 8 == 0 && spec->vdim <= 128 &&
         reinterpret_cast<uintptr_t>(cache) % 16 == 0) {
         // Few rows per request in bfloat16: the query heads of a kv head share one block (and one reading of the keys).
         const size_t stages = sizeof(__nv_bfloat16) * (static_cast<size_t>(16 + 2 * kKeys) * (spec->dim + kPad) +
                                                        (spec->shared_kv ? 0 : 2 * kKeys * (spec->vdim + kPad)));
         const size_t sums = sizeof(__nv_bfloat16) * 16 * (spec->dim + kPad) + sizeof(float) * 4 * 16 * (spec->vdim + 2);
         const size_t group_shared = stages > sums ? stages : sums;
-        const dim3 group_grid(rows, spec->kv_heads, max_splits);
+        const dim3 group_grid(rows, spec->kv_heads * ((group + 15) / 16), max_splits);     // more than 16 heads on a kv head: 16 a block
 #define MLR_GROUP(NV)                                                                                                                       \
     do {                                                                                                                                    \
         cudaFuncSetAttribute(attention_masked_group_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(group_shared)); \

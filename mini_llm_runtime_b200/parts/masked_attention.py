@@ -193,10 +193,14 @@ def emit_masked_attention(b, desc: MaskedAttentionSpec, q, gate, act, run: RunCo
     # floats lets the kernel cut every planned range into FINER (its blocks wait for memory most of the time, and
     # more of them in flight is what makes a long context fast; the planner's own split is tuned for a kernel that
     # copies keys in bulk).
+    # Where more than 16 query heads share a kv head (latent attention: all of them), the few-row kernel takes them 16 at a
+    # time in blocks of their own: the planner is told of that many more kv heads, each shared by 16 (a few-row segment is then
+    # ONE row, a decoded token), and sizes the ranges' scratch for them.
     group = heads // kv_heads
-    plan = b.plan((group if group <= 16 else 1, kv_heads, 0, 0, finer * (max(dim, vdim) + 2), 1))
+    chunks = (group + 15) // 16
+    plan = b.plan((min(group, 16), kv_heads * chunks, 0, 0, finer * (max(dim, vdim) + 2), 1))
     info = b.meta("segment_info")
-    split = (plan.chunk, plan.max_splits, finer, plan.scratch) if group <= 16 else (0, 1, 1, None)
+    split = (plan.chunk, plan.max_splits, finer, plan.scratch)
     b.launch("attention_masked", "mlr_attention_masked", *args, 1, *where, b.meta("positions"), b.meta("segment_of_row"), table,
              stride, b.page_size, 0, plan.items, plan.n_items, info, *split, b.status, b.stream, need=plan.n_items)
     b.launch("attention_masked", "mlr_attention_masked_tiles", *args, *where, plan.tiles, plan.n_tiles, info, table, stride,

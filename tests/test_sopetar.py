@@ -164,7 +164,8 @@ def _attend(spec, q, gate, out, cache, n_pages, table, page, T, how, kv_heads, v
     else:
         _, last, keys, most, finer = how
         info = torch.tensor([[T - last, last, T - last, 0]], dtype=torch.int32, device=dev)
-        partial = torch.full((16 * kv_heads * most * finer * (vdim + 2),), float("nan"), device=dev)
+        slots = max(16 * kv_heads, -(-spec.heads // 16) * 16)       # more than 16 heads on a kv head: one row, heads rounded up to 16
+        partial = torch.full((slots * most * finer * (vdim + 2),), float("nan"), device=dev)
         _call("attention_masked", "mlr_attention_masked", *common, is16, cache.data_ptr(), n_pages, positions.data_ptr(), of_row.data_ptr(),
               table.data_ptr(), table.stride(0), page, 0, None, 1, info.data_ptr(), keys, most, finer, partial.data_ptr(), status.data_ptr(),
               native.stream())
@@ -430,6 +431,10 @@ def _latent_case(dtype, heads, dim, rot, vdim, rank, T, page, how="rows", window
     dict(heads=4, dim=16, rot=16, vdim=8, rank=48, T=333, page=16, window=70, how=("split", 3, 64, 6, 1)),
     dict(heads=2, dim=32, rot=32, vdim=16, rank=32, T=700, page=16, window=300, how=("split", 1, 128, 6, 4), base=500.0),
     dict(heads=2, dim=8, rot=0, vdim=8, rank=16, T=60, page=16, window=20),
+    # more than 16 heads on the one kv head: a decoded token's heads are taken 16 at a time, with and without ranges of keys
+    dict(heads=20, dim=16, rot=16, vdim=8, rank=48, T=333, page=16, window=70, how=("split", 1, 64, 6, 1)),
+    dict(heads=35, dim=8, rot=8, vdim=8, rank=24, T=210, page=8, how=("split", 1, 64, 1, 1)),
+    dict(heads=33, dim=16, rot=16, vdim=8, rank=32, T=500, page=16, window=260, how=("split", 1, 128, 3, 4), base=500.0),
 ])
 def test_latent_attention_with_a_rotated_key_part_a_window_a_sink_and_a_gate(dtype, case):
     got, want, *_ = _latent_case(dtype, **case)
