@@ -90,7 +90,15 @@ ONLY_ATTENTION = {
                _attention(4, 1, 8, 16, 0.5, None, softcap=5.0, v_mix=True)],
 }
 
-ALL = {"small_a": SMALL_A, "small_b": SMALL_B, "small_c": SMALL_C, "only_latent": ONLY_LATENT, "only_attention": ONLY_ATTENTION}
+# More than 16 query heads on a kv head in both mixers (the latent mixer has one kv head for all of its heads), with sizes the
+# tensor-core kernels take: decoded tokens run their heads 16 at a time.
+MANY_HEADS = {
+    "architecture": "Sopetar", "vocab": 75, "width": 40, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.8},
+    "layers": [_latent(18, 16, 16, 8, 8, 32, 0.2, 21, _dense(24, 1.5)),
+               _attention(34, 2, 16, 8, 0.5, _dense(24, 2.0), window=30, keep_first=3, softcap=6.0)],
+}
+
+ALL = {"small_a": SMALL_A, "many_heads": MANY_HEADS, "small_b": SMALL_B, "small_c": SMALL_C, "only_latent": ONLY_LATENT, "only_attention": ONLY_ATTENTION}
 
 
 def get(name: str) -> dict:
