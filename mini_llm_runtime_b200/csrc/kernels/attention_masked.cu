@@ -761,7 +761,7 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
 // end the warps' results are added up in shared memory and go to `partial` in the row kernel's layout (the same merge
 // kernel follows), or, when the block has seen every key of the row, straight to the output.
 template <int NV>
-__global__ void __launch_bounds__(128) attention_masked_group_kernel(const __nv_bfloat16* q, int ldq, const __nv_bfloat16* gate, int ld_gate,
+__global__ void __launch_bounds__(128, NV >= 16 ? 3 : 4) attention_masked_group_kernel(const __nv_bfloat16* q, int ldq, const __nv_bfloat16* gate, int ld_gate,
                                                                      __nv_bfloat16* out, int ldo, const __nv_bfloat16* cache, int num_pages,
                                                                      const int* positions, const int* segment_of_row, const int* block_table,
                                                                      int table_stride, int page_size, MaskedAttentionSpec s, const int* items,
