@@ -4,7 +4,7 @@ heads that share key/value heads and heads of their own, key and value sizes tha
 and larger than the rotated dimensions, latents that are no multiple of 8, windows of 1, of a few tokens, of more
 than a tile of keys, larger than every prompt, and none; kept first tokens fewer than, equal to and more than the
 window, and none; layers with and without a cap on the scores, with and without value mixing (none, one, several
-such layers), with and without a feed-forward, with and without a clamp in it."""
+such layers), with and without a feed-forward, with and without a clamp in it; one has more than 16 query heads on a kv head."""
 from __future__ import annotations
 
 import copy
