@@ -338,7 +338,32 @@ def sopetar_config(width, ff, heads, kv, dim, layers, chunk, vocab):
                        for i in range(layers)]}
 
 
-DESIGNS = {"gopevik": gopevik_config, "niridra": niridra_config, "sopetar": sopetar_config}
+def sokolorn_config(width, ff, heads, kv, dim, layers, chunk, vocab):
+    """Sub-layers that read the stream itself with their norm behind them.  In turn: attention without rotation (q and k normed
+    over the whole projection, a window of half the context, learned sinks, a gate per head) with a squared-relu feed-forward
+    of 1.5 x ff (two matrices instead of three: the dense layer's parameters); attention with biases, per-head q/k norm and
+    rotation of half of each head with slowed long wavelengths, with sixteen routed experts of ff / 6 of which four are used
+    beside a shared one of ff / 3 (clamped gates, softmax over the chosen logits); the same attention reading the keys and values
+    of the layer before it, dense; the first kind again with experts.  Logits from the embedding table, capped."""
+    windowed = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": max(chunk // 2, 1)}}
+    rotary = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+              "rot": {"base": 5e5, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}}}
+    dense = {"kind": "dense", "ff": ff * 3 // 2}
+    moe = {"kind": "moe", "expert": {"ff": ff // 6, "limit": 7.0}, "shared": {"ff": ff // 3, "limit": 7.0}, "router": {"experts": 16, "top": 4}}
+    made = []
+    for i in range(layers):
+        if i % 4 == 2:
+            made.append({"type": "attention_2", "mixer": dict(rotary, kv_from=i - 1), "mlp": dense})
+        elif i % 4 == 1:
+            made.append({"type": "attention_2", "mixer": rotary, "mlp": moe})
+        else:
+            made.append({"type": "attention", "mixer": windowed, "mlp": moe if i % 4 == 3 else dense})
+    return {"architecture": "Sokolorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": made}
+
+
+DESIGNS = {"gopevik": gopevik_config, "niridra": niridra_config, "sopetar": sopetar_config, "sokolorn": sokolorn_config}
+# The package's other design that stands nearest (the same attention kernels), measured as a second neighbour.
+NEIGHBOUR = {"niridra": "gopevik", "sopetar": "gopevik", "sokolorn": "sopetar"}
 
 
 def compare_designs(args) -> int:
@@ -405,9 +430,9 @@ def compare_designs(args) -> int:
             results[name] = {args.compare: g, "qwen3": q,
                              "prefill_ratio": g["prefill_tokens_per_s"] / q["prefill_tokens_per_s"],
                              "decode_ratio": g["decode_tokens_per_s"] / q["decode_tokens_per_s"]}
-            if args.compare != "gopevik":       # the other hybrid design of the package, as a second neighbour
-                other = measure(gopevik_config(width, ff, heads, kv, dim, layers, context, vocab))
-                results[name]["gopevik"] = other
+            if args.compare in NEIGHBOUR:       # another hybrid design of the package, as a second neighbour
+                other = measure(DESIGNS[NEIGHBOUR[args.compare]](width, ff, heads, kv, dim, layers, context, vocab))
+                results[name][NEIGHBOUR[args.compare]] = other
     print(json.dumps({"metric": f"prefill and decode tok/s of the {args.compare.capitalize()} design beside Qwen3 at equal layer sizes", "unit": "tokens/s",
                       "layers": layers, "context": context, "batch": batch, "steps": steps, "warmup": warmup, "dtype": "bf16",
                       "data": "synthetic", "sizes": results, "clocks": clocks.summary()}))

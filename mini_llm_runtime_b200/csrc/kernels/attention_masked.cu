@@ -30,11 +30,14 @@ struct MaskedAttentionSpec {
     const float* freq;     // [rot_dims / 2] float32 on the device, or null
     const float* sinks;    // [heads] float32 on the device: the sink's score per head; null with sink set: 0
     const float* slopes;   // [heads] float32 on the device: score -= slopes[head] * distance; null: no such bias
+    const float* q_weight; // the weights of a norm of q and of k that `mlr_qkv_prepare_cache` applies (float32 on the device):
+    const float* k_weight; // qk_norm 1: [dim] each, shared by all heads; qk_norm 2: [heads * dim] and [kv_heads * dim]
     int heads, kv_heads, dim, vdim;
     int rot_dims, window, chunk, sink;
     int gate_kind;         // 0 none, 1 sigmoid, 2 silu, 3 sigmoid of one value per head (the gate has `heads` columns)
     int shared_kv;         // 1: a token's value is the first vdim values of its key (vdim <= dim; one vector per token is cached and a page holds keys only)
     int keep_first;        // with a window: the first keep_first positions stay visible
+    int qk_norm;           // 0 none; 1 every head of q and k over its root mean square, times a weight; 2 the WHOLE projection (all heads) likewise
     float scale, out_scale;
     float softcap;         // > 0: score <- softcap * tanh(score / softcap)
 };
@@ -105,9 +108,13 @@ __global__ void __launch_bounds__(kThreads) kv_rope_cache_kernel(const T* k, int
 }
 
 // The step's q, k and v as the projection left them, made ready for attention, blocks of four warps per row and one warp per head:
-//   q_h <- (q_h + bias) / rms(q_h)          in place         (biases and the division only where asked for)
-//   k_g <- (k_g + bias) / rms(k_g), rotated like `kv_rope_cache_kernel` does, into the cache
+//   q_h <- norm(q_h + bias)                  in place         (biases and the norm only where asked for)
+//   k_g <- norm(k_g + bias), rotated like `kv_rope_cache_kernel` does, into the cache
 //   v_g <- (v_g + bias) / rms(v_g);  mix 1: first[row] = v;  mix 2: v <- (1 - lambda) v + lambda first[row];  into the cache
+// norm of q and k: unit_qk divides every head by its root mean square; qk_norm 1 does so and multiplies by a weight of one head's
+// size that all heads share (wq, wk [dim]); qk_norm 2 divides the WHOLE projection (all heads of q, all heads of k) by its root
+// mean square and multiplies by a weight of the projection's size (wq [heads * dim], wk [kv_heads * dim]; one block a row then).
+// Without k (a layer that reads the keys and values another layer cached) only the queries are prepared.
 // `first` is a float32 buffer of the step, [rows, kv_heads * vdim]: the values the first of several layers made of the same
 // tokens, which the later ones mix into their own.  All arithmetic is float32.
 template <typename T>
@@ -116,14 +123,22 @@ __global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int l
                                                                      float* first, int ld_first, int mix, float lambda, T* cache, int num_pages,
                                                                      const int* positions, const int* segment_of_row, const int* block_table,
                                                                      int table_stride, int page_size, MaskedAttentionSpec s, int* status) {
+    const float* wq = s.q_weight;
+    const float* wk = s.k_weight;
+    const int qk_norm = s.qk_norm;
     mlr_grid_wait();
     extern __shared__ __align__(16) float staged[];        // [warps][max(dim, vdim)]
+    __shared__ float whole_sum[kThreads / 32];
+    __shared__ float whole_inv[2];
     const int row = blockIdx.x;
     const int position = positions[row];
-    const int page = block_table[static_cast<size_t>(segment_of_row[row]) * table_stride + position / page_size];
-    if (page < 0 || page >= num_pages) {
-        if (threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
-        return;
+    int page = 0;
+    if (k) {
+        page = block_table[static_cast<size_t>(segment_of_row[row]) * table_stride + position / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
+            return;
+        }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* mine = staged + warp * max(s.dim, s.vdim);
@@ -133,7 +148,30 @@ __global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int l
                static_cast<size_t>(position % page_size) * s.vdim;
     const int half = s.rot_dims / 2;
     const float p = static_cast<float>(position);
-    for (int unit = blockIdx.y * (kThreads / 32) + warp; unit < s.heads + 2 * s.kv_heads; unit += gridDim.y * (kThreads / 32)) {
+    if (qk_norm == 2) {
+        // The root mean square of a whole projection: every thread sums its columns, the warps' sums are added in order.
+        for (int which = 0; which < (k ? 2 : 1); ++which) {
+            const T* src = which == 0 ? q + static_cast<size_t>(row) * ldq : k + static_cast<size_t>(row) * ld_k;
+            const float* bias = which == 0 ? bq : bk;
+            const int total = (which == 0 ? s.heads : s.kv_heads) * s.dim;
+            float squares = 0.0f;
+            for (int c = threadIdx.x; c < total; c += kThreads) {
+                const float value = mlr_load(src, c) + (bias ? bias[c] : 0.0f);
+                squares = fmaf(value, value, squares);
+            }
+            squares = mlr_warp_sum(squares);
+            if (lane == 0) whole_sum[warp] = squares;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float sum = 0.0f;
+                for (int w = 0; w < kThreads / 32; ++w) sum += whole_sum[w];
+                whole_inv[which] = 1.0f / sqrtf(sum / static_cast<float>(total) + eps);
+            }
+            __syncthreads();
+        }
+    }
+    const int units = k ? s.heads + 2 * s.kv_heads : s.heads;
+    for (int unit = blockIdx.y * (kThreads / 32) + warp; unit < units; unit += gridDim.y * (kThreads / 32)) {
         const int kind = unit < s.heads ? 0 : (unit < s.heads + s.kv_heads ? 1 : 2);
         const int head = kind == 0 ? unit : (kind == 1 ? unit - s.heads : unit - s.heads - s.kv_heads);
         const int n = kind == 2 ? s.vdim : s.dim;
@@ -146,20 +184,28 @@ __global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int l
             mine[c] = value;
             squares = fmaf(value, value, squares);
         }
-        const bool unit_norm = kind == 2 ? unit_v : unit_qk;
-        const float inv = unit_norm ? 1.0f / sqrtf(mlr_warp_sum(squares) / static_cast<float>(n) + eps) : 1.0f;
+        const bool head_norm = kind == 2 ? unit_v : (unit_qk || qk_norm == 1);
+        float inv = head_norm ? 1.0f / sqrtf(mlr_warp_sum(squares) / static_cast<float>(n) + eps) : 1.0f;
+        const float* weight = nullptr;
+        if (kind < 2 && qk_norm == 2) {
+            inv = whole_inv[kind];
+            weight = (kind == 0 ? wq : wk) + static_cast<size_t>(head) * n;
+        } else if (kind < 2 && qk_norm == 1) {
+            weight = kind == 0 ? wq : wk;
+        }
+        for (int c = lane; c < n; c += 32) mine[c] = mine[c] * inv * (weight ? weight[c] : 1.0f);     // a lane's own values
         __syncwarp();
         if (kind == 0) {
             T* dst = q + static_cast<size_t>(row) * ldq + static_cast<size_t>(head) * n;
-            for (int c = lane; c < n; c += 32) mlr_store(dst, c, mine[c] * inv);
+            for (int c = lane; c < n; c += 32) mlr_store(dst, c, mine[c]);
         } else if (kind == 1) {
             T* dst = kbase + static_cast<size_t>(head) * page_size * s.dim;
             for (int c = lane; c < n; c += 32) {
-                float value = mine[c] * inv;
+                float value = mine[c];
                 if (c < s.rot_dims) {
                     float sn, cs;
                     sincosf(p * s.freq[c < half ? c : c - half], &sn, &cs);
-                    const float other = mine[c < half ? c + half : c - half] * inv;
+                    const float other = mine[c < half ? c + half : c - half];
                     value = c < half ? value * cs - other * sn : value * cs + other * sn;
                 }
                 mlr_store(dst, c, value);
@@ -168,7 +214,7 @@ __global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int l
             T* dst = vbase + static_cast<size_t>(head) * page_size * s.vdim;
             float* keep = first ? first + static_cast<size_t>(row) * ld_first + static_cast<size_t>(head) * n : nullptr;
             for (int c = lane; c < n; c += 32) {
-                float value = mine[c] * inv;
+                float value = mine[c];
                 if (mix == 1) keep[c] = value;
                 else if (mix == 2) value = (1.0f - lambda) * value + lambda * __ldcg(keep + c);
                 mlr_store(dst, c, value);
@@ -1075,22 +1121,32 @@ MLR_API int mlr_kv_rope_cache(const MaskedAttentionSpec* spec, const void* k, in
 
 // q, k, v: the step's projections (q is changed in place); bq, bk, bv: float32 biases or null; first: float32 [rows, kv_heads * vdim]
 // (row stride ld_first) with mix 1 (written) or 2 (read), else null.  Not for caches whose values are their keys.
+// The description's qk_norm, q_weight and k_weight name a weighted norm of q and k.  With k, v and cache null the layer reads another layer's cache and only its queries are prepared.
 MLR_API int mlr_qkv_prepare_cache(const MaskedAttentionSpec* spec, void* q, int ldq, const void* k, int ld_k, const void* v, int ld_v, int act_bf16,
                                   const float* bq, const float* bk, const float* bv, int unit_qk, int unit_v, float eps, float* first, int ld_first,
                                   int mix, float lambda, void* cache, int num_pages, const int* positions, const int* segment_of_row,
                                   const int* block_table, int table_stride, int page_size, int rows, int* status, cudaStream_t stream) {
     if (check_spec(spec, "qkv_prepare_cache")) return 1;
-    MLR_REQUIRE(rows >= 0 && page_size > 0 && num_pages > 0 && cache && block_table && q && k && v, "qkv_prepare_cache: bad sizes or no cache");
+    const bool own_kv = k != nullptr;
+    const float* wq = spec->q_weight;
+    const float* wk = spec->k_weight;
+    const int qk_norm = spec->qk_norm;
+    MLR_REQUIRE(rows >= 0 && page_size > 0 && q, "qkv_prepare_cache: bad sizes or no queries");
+    MLR_REQUIRE(own_kv ? (v && cache && block_table && num_pages > 0) : (!v && !cache && mix == 0),
+                "qkv_prepare_cache: keys, values and the cache come together or not at all");
     MLR_REQUIRE(!spec->shared_kv, "qkv_prepare_cache: this cache keeps keys and values apart");
-    MLR_REQUIRE(ldq >= spec->heads * spec->dim && ld_k >= spec->kv_heads * spec->dim && ld_v >= spec->kv_heads * spec->vdim,
+    MLR_REQUIRE(ldq >= spec->heads * spec->dim && (!own_kv || (ld_k >= spec->kv_heads * spec->dim && ld_v >= spec->kv_heads * spec->vdim)),
                 "qkv_prepare_cache: a row stride is smaller than the row");
     MLR_REQUIRE(mix >= 0 && mix <= 2 && (mix == 0 || (first && ld_first >= spec->kv_heads * spec->vdim)), "qkv_prepare_cache: mixing needs the first values' buffer");
+    MLR_REQUIRE(qk_norm >= 0 && qk_norm <= 2 && (qk_norm == 0 || (wq && (wk || !own_kv) && eps > 0.0f)),
+                "qkv_prepare_cache: a weighted norm of q and k needs its weights and a positive eps");
     if (rows == 0) return 0;
     const size_t shared = sizeof(float) * (kThreads / 32) * static_cast<size_t>(spec->dim > spec->vdim ? spec->dim : spec->vdim);
     // With few rows (decoded tokens) every warp takes one head of q, k or v; with many, a block of four warps walks its row's
-    // heads in turn, which the same number of blocks in flight does a little faster.
-    const int units = spec->heads + 2 * spec->kv_heads, warps = kThreads / 32;
-    const int wanted = rows >= 592 ? 1 : (592 + rows - 1) / rows, most = (units + warps - 1) / warps;
+    // heads in turn, which the same number of blocks in flight does a little faster.  A norm over the whole projection reads all
+    // of q before any of it is changed: one block a row.
+    const int units = own_kv ? spec->heads + 2 * spec->kv_heads : spec->heads, warps = kThreads / 32;
+    const int wanted = rows >= 592 || qk_norm == 2 ? 1 : (592 + rows - 1) / rows, most = (units + warps - 1) / warps;
     const dim3 grid(rows, wanted < most ? wanted : most);
     if (act_bf16)
         mlr_launch((qkv_prepare_cache_kernel<__nv_bfloat16>), dim3(grid), dim3(kThreads), shared, stream, static_cast<__nv_bfloat16*>(q), ldq,

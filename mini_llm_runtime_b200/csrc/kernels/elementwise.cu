@@ -742,3 +742,87 @@ MLR_API int mlr_swiglu_sliced(const float* partials, int slices, long long slice
                                                          static_cast<float*>(out), rows, inter, block);
     return mlr_launched("swiglu_sliced");
 }
+
+// An activation without a gate, row by row: out = act(in).  kind 0: relu(x)^2; 1: the tanh form of GELU; 2: SiLU.
+namespace {
+__device__ __forceinline__ float plain_activation(float x, int kind) {
+    if (kind == 0) {
+        const float r = fmaxf(x, 0.0f);
+        return r * r;
+    }
+    if (kind == 1) return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    return x / (1.0f + expf(-x));
+}
+
+template <typename T>
+__global__ void activation_vec8_kernel(const T* in, int ld, T* out, int ld_out, int width, int kind) {
+    mlr_grid_wait();
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q < (width >> 3)) {
+        const size_t r = blockIdx.y, c = static_cast<size_t>(q) * 8;
+        float v[8];
+        mlr_load8(in + r * ld + c, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = plain_activation(v[e], kind);
+        mlr_store8(out + r * ld_out + c, v);
+    }
+    mlr_grid_dependents_may_start();
+}
+
+template <typename T>
+__global__ void activation_kernel(const T* in, int ld, T* out, int ld_out, int rows, int width, int kind) {
+    mlr_grid_wait();
+    const size_t total = static_cast<size_t>(rows) * width;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t r = i / width, c = i - r * width;
+        mlr_store(out, r * ld_out + c, plain_activation(mlr_load(in, r * ld + c), kind));
+    }
+    mlr_grid_dependents_may_start();
+}
+}  // namespace
+
+// in, out: [rows, width] in the activations' precision (row strides ld, ld_out; they may be the same buffer).
+MLR_API int mlr_activation(const void* in, int ld, void* out, int ld_out, int act_bf16, int rows, int width, int kind, cudaStream_t stream) {
+    MLR_REQUIRE(rows >= 0 && width > 0 && ld >= width && ld_out >= width, "activation: bad sizes rows=%d width=%d", rows, width);
+    MLR_REQUIRE(kind >= 0 && kind <= 2, "activation: unknown kind %d", kind);
+    if (rows == 0) return 0;
+    const int unit = act_bf16 ? 8 : 4;          // values in 16 bytes
+    if (width % 8 == 0 && ld % unit == 0 && ld_out % unit == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0 &&
+        reinterpret_cast<uintptr_t>(out) % 16 == 0 && rows <= 65535) {
+        const dim3 grid((width / 8 + 127) / 128, rows);
+        if (act_bf16)
+            mlr_launch((activation_vec8_kernel<__nv_bfloat16>), dim3(grid), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(in), ld,
+                       static_cast<__nv_bfloat16*>(out), ld_out, width, kind);
+        else
+            mlr_launch((activation_vec8_kernel<float>), dim3(grid), dim3(128), 0, stream, static_cast<const float*>(in), ld,
+                       static_cast<float*>(out), ld_out, width, kind);
+        return mlr_launched("activation");
+    }
+    const int blocks = mlr_grid_stride_blocks(static_cast<size_t>(rows) * width / 1024 + 1, 16);
+    if (act_bf16)
+        mlr_launch((activation_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), ld,
+                   static_cast<__nv_bfloat16*>(out), ld_out, rows, width, kind);
+    else
+        mlr_launch((activation_kernel<float>), dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(in), ld,
+                   static_cast<float*>(out), ld_out, rows, width, kind);
+    return mlr_launched("activation");
+}
+
+// logits <- cap * tanh(logits / cap), float32 [rows, width] in place (a cap on the output head's scores).
+namespace {
+__global__ void softcap_kernel(float* x, size_t total, float cap) {
+    mlr_grid_wait();
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        x[i] = cap * tanhf(x[i] / cap);
+    mlr_grid_dependents_may_start();
+}
+}  // namespace
+
+MLR_API int mlr_softcap(float* x, int rows, int width, float cap, cudaStream_t stream) {
+    MLR_REQUIRE(rows >= 0 && width > 0 && cap > 0.0f, "softcap: bad sizes or cap");
+    if (rows == 0) return 0;
+    const size_t total = static_cast<size_t>(rows) * width;
+    mlr_launch(softcap_kernel, dim3(mlr_grid_stride_blocks(total / 1024 + 1, 16)), dim3(256), 0, stream, x, total, cap);
+    return mlr_launched("softcap");
+}

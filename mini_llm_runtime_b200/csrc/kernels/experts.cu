@@ -15,6 +15,9 @@
 //             so a token's result does not depend on which other tokens share its tile.
 //   combine   out[token] = sum_j weight_j y[row of (token, j)]  (+ shared gate * shared expert's result), j in
 //             the order of the choice.
+// A second kind of router (`kind` 1): z = R x + bias (the `correction` operand), the `top` largest z are chosen (ties to
+// the lower index) and their weights are the softmax over the chosen z alone; no groups.  A second shape of the gate
+// (`gated` 2): g <- min(g, limit), u <- clamp(u, -limit, limit) where limit > 0, then g * sigmoid(alpha g) * (u + up_offset).
 #include "common.cuh"
 
 namespace {
@@ -26,10 +29,26 @@ constexpr int kTileRows = 32;     // rows of one expert per block of a product
 constexpr int kTileCols = 64;
 constexpr int kTileK = 16;
 
+// What the two products of a gated expert become.  kind 1: silu(g) * u.  kind 2: see the head of this file.
+struct ExpertGate {
+    int kind;
+    float alpha, limit, up_offset;
+};
+__device__ __forceinline__ float expert_gate(float g, float u, const ExpertGate& shape) {
+    if (shape.kind == 2) {
+        if (shape.limit > 0.0f) {
+            g = fminf(g, shape.limit);
+            u = fminf(fmaxf(u, -shape.limit), shape.limit);
+        }
+        return g / (1.0f + expf(-shape.alpha * g)) * (u + shape.up_offset);
+    }
+    return g / (1.0f + expf(-g)) * u;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* x, long long ld, const float* router, const float* correction,
                                                               int width, int experts, int groups, int keep, int top, int has_gate,
-                                                              int* chosen, float* weights, int* place, int* counts, float* shared_gate) {
+                                                              int* chosen, float* weights, int* place, int* counts, float* shared_gate, int kind) {
     mlr_grid_wait();
     extern __shared__ __align__(16) float shared[];
     float* xs = shared;                 // [width]
@@ -61,11 +80,13 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* x, long l
         sum = mlr_warp_sum(sum);
         if (lane == 0) {
             const float s = 1.0f / (1.0f + expf(-sum));
-            if (e < experts) {
+            if (e >= experts) {
+                shared_gate[row] = s;
+            } else if (kind == 1) {
+                score[e] = choice[e] = sum + (correction ? correction[e] : 0.0f);
+            } else {
                 score[e] = s;
                 choice[e] = s + (correction ? correction[e] : 0.0f);
-            } else {
-                shared_gate[row] = s;
             }
         }
     }
@@ -109,6 +130,15 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* x, long l
         taken[k] = best;
         picked[k] = score[best];
         total += score[best];
+    }
+    if (kind == 1) {
+        // softmax over the chosen logits alone; the first chosen is the largest
+        const float largest = picked[0];
+        total = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            picked[k] = expf(picked[k] - largest);
+            total += picked[k];
+        }
     }
     total_score = total;
     }
@@ -163,7 +193,7 @@ __global__ void __launch_bounds__(1024) arrange_kernel(int* counts, const int* c
 // DUAL: two matrices (gate and up) and out = silu(gate) * up in TO; else the product itself in TO.
 template <typename T, typename TO, bool DUAL>
 __global__ void __launch_bounds__(256) expert_product_kernel(const T* a, long long lda, const int* source, int divisor, const T* w, const T* w2,
-                                                             int N, int K, TO* out, long long ldo, const int* tiles, const int* n_tiles) {
+                                                             int N, int K, TO* out, long long ldo, const int* tiles, const int* n_tiles, ExpertGate shape) {
     mlr_grid_wait();
     const int tile = blockIdx.y;
     if (tile >= __ldcg(n_tiles)) return;
@@ -223,7 +253,7 @@ __global__ void __launch_bounds__(256) expert_product_kernel(const T* a, long lo
             const int c = col0 + tx + 16 * j;
             if (c >= N) continue;
             float value = acc[i][j];
-            if (DUAL) value = value / (1.0f + expf(-value)) * acc2[i][j];
+            if (DUAL) value = expert_gate(value, acc2[i][j], shape);
             mlr_store(orow, c, value);
         }
     }
@@ -267,7 +297,7 @@ template <typename TO, bool DUAL, int BM>
 __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bfloat16* a, long long lda, const int* source, int divisor,
                                                                  const __nv_bfloat16* w, const __nv_bfloat16* w2, int N, int K, TO* out,
                                                                  long long ldo, const int* tiles, const int* n_tiles, int all_rows,
-                                                                 int a_step, int out_step) {
+                                                                 int a_step, int out_step, ExpertGate shape) {
     mlr_grid_wait();
     // With a tile list: tile blockIdx.y of it.  Without: every matrix (blockIdx.z) takes all `all_rows` rows, its inputs `a_step`
     // columns and its outputs `out_step` columns further right than those of the matrix before.
@@ -376,7 +406,7 @@ __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bflo
             for (int j = 0; j < 2; ++j) {
                 if (c + j >= N) continue;
                 float value = acc[mt][piece][2 * half + j];
-                if (DUAL) value = value / (1.0f + expf(-value)) * acc2[DUAL ? mt : 0][DUAL ? piece : 0][2 * half + j];
+                if (DUAL) value = expert_gate(value, acc2[DUAL ? mt : 0][DUAL ? piece : 0][2 * half + j], shape);
                 mlr_store(orow, c + j, value);
             }
         }
@@ -414,7 +444,8 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* y, long long 
 // the call (`mlr_experts_arrange` zeroes them again).  chosen, place: int32 [rows, top]; weights: float32 [rows, top]; shared_gate [rows].
 MLR_API int mlr_experts_route(const void* x, long long ld, int act_bf16, const float* router, const float* correction, int rows, int width,
                               int experts, int groups, int keep, int top, int has_gate, int* chosen, float* weights, int* place, int* counts,
-                              float* shared_gate, cudaStream_t stream) {
+                              float* shared_gate, int kind, cudaStream_t stream) {
+    MLR_REQUIRE(kind == 0 || (kind == 1 && groups == 1), "experts_route: unknown kind of router %d (or one that has no groups)", kind);
     MLR_REQUIRE(x && router && chosen && weights && place && counts && width > 0, "experts_route: bad arguments");
     MLR_REQUIRE(experts >= 1 && experts <= kMaxExperts && top >= 1 && top <= kMaxTop && top <= experts, "experts_route: %d of %d experts (at most %d of %d)",
                 top, experts, kMaxTop, kMaxExperts);
@@ -429,11 +460,11 @@ MLR_API int mlr_experts_route(const void* x, long long ld, int act_bf16, const f
     if (act_bf16) {
         if (shared > 48 * 1024) cudaFuncSetAttribute(route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
         mlr_launch((route_kernel<__nv_bfloat16>), dim3(rows), dim3(threads), shared, stream, static_cast<const __nv_bfloat16*>(x), ld, router,
-                   correction, width, experts, groups, keep, top, has_gate, chosen, weights, place, counts, shared_gate);
+                   correction, width, experts, groups, keep, top, has_gate, chosen, weights, place, counts, shared_gate, kind);
     } else {
         if (shared > 48 * 1024) cudaFuncSetAttribute(route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
         mlr_launch((route_kernel<float>), dim3(rows), dim3(threads), shared, stream, static_cast<const float*>(x), ld, router, correction, width,
-                   experts, groups, keep, top, has_gate, chosen, weights, place, counts, shared_gate);
+                   experts, groups, keep, top, has_gate, chosen, weights, place, counts, shared_gate, kind);
     }
     return mlr_launched("experts_route");
 }
@@ -468,11 +499,14 @@ MLR_API int mlr_experts_tensor_cores(int K, long long lda) { return K % 8 == 0 &
 
 // a: [*, K] activations (bfloat16 or float32), row r of the product is row source[r] / divisor of `a` (or r without `source`).
 // w (and w2 when `gated`): [experts, N, K] in the activations' precision.  out: [pairs, N]; float32 when out_f32, else the
-// activations' precision; with `gated` out = silu(a w^T) * (a w2^T).  The product has rows * top rows.
+// activations' precision; with `gated` 1 out = silu(a w^T) * (a w2^T), with `gated` 2 the clamped shape of alpha, limit and
+// up_offset (see the head of this file).  The product has rows * top rows.
 MLR_API int mlr_experts_product(const void* a, long long lda, int act_bf16, const int* source, int divisor, const void* w, const void* w2, int gated,
                                 int N, int K, void* out, long long ldo, int out_f32, const int* tiles, const int* n_tiles, int rows, int top, int experts,
-                                int tile_rows, cudaStream_t stream) {
+                                int tile_rows, float alpha, float limit, float up_offset, cudaStream_t stream) {
     const int pairs = rows * top;
+    MLR_REQUIRE(gated >= 0 && gated <= 2, "experts_product: unknown gate %d", gated);
+    const ExpertGate shape = {gated, alpha, limit, up_offset};
     MLR_REQUIRE(a && w && out && tiles && n_tiles && N > 0 && K > 0 && (!gated || w2) && (!source || divisor > 0), "experts_product: bad arguments");
     const bool tensor_cores = act_bf16 && K % 8 == 0 && lda % 8 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 &&
                               reinterpret_cast<uintptr_t>(w) % 16 == 0 && (!gated || reinterpret_cast<uintptr_t>(w2) % 16 == 0) && !mlr_experts_simt_only();
@@ -491,7 +525,7 @@ MLR_API int mlr_experts_product(const void* a, long long lda, int act_bf16, cons
         cudaFuncSetAttribute(expert_product_mma_kernel<TO, DUAL, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,                         \
                              static_cast<int>(mma_shared_bytes(BM, DUAL)));                                                                \
         mlr_launch((expert_product_mma_kernel<TO, DUAL, BM>), dim3(wide), dim3(256), mma_shared_bytes(BM, DUAL), stream, ab, lda, source,  \
-                   divisor, wb, w2b, N, K, static_cast<TO*>(out), ldo, tiles, n_tiles, 0, 0, 0);                                           \
+                   divisor, wb, w2b, N, K, static_cast<TO*>(out), ldo, tiles, n_tiles, 0, 0, 0, shape);                                    \
     } while (0)
         if (gated && !out_f32) {
             if (tile_rows == 64) MLR_MMA(__nv_bfloat16, true, 64);
@@ -507,7 +541,7 @@ MLR_API int mlr_experts_product(const void* a, long long lda, int act_bf16, cons
     }
 #define MLR_GO(T, TO, DUAL)                                                                                                              \
     mlr_launch((expert_product_kernel<T, TO, DUAL>), dim3(grid), dim3(256), 0, stream, static_cast<const T*>(a), lda, source, divisor,   \
-               static_cast<const T*>(w), static_cast<const T*>(w2), N, K, static_cast<TO*>(out), ldo, tiles, n_tiles)
+               static_cast<const T*>(w), static_cast<const T*>(w2), N, K, static_cast<TO*>(out), ldo, tiles, n_tiles, shape)
     if (act_bf16) {
         if (gated && !out_f32) MLR_GO(__nv_bfloat16, __nv_bfloat16, true);
         else if (!gated && out_f32) MLR_GO(__nv_bfloat16, float, false);
@@ -536,13 +570,13 @@ MLR_API int mlr_batched_product_bf16_strided(const void* a, long long lda, int a
         cudaFuncSetAttribute(expert_product_mma_kernel<__nv_bfloat16, false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(mma_shared_bytes(64, false)));
         mlr_launch((expert_product_mma_kernel<__nv_bfloat16, false, 64>), dim3(grid), dim3(256), mma_shared_bytes(64, false), stream, ab, lda, none, 1,
-                   wb, wb, N, K, static_cast<__nv_bfloat16*>(out), ldo, none, none, rows, a_step, out_step);
+                   wb, wb, N, K, static_cast<__nv_bfloat16*>(out), ldo, none, none, rows, a_step, out_step, ExpertGate{0, 0.0f, 0.0f, 0.0f});
     } else {
         const dim3 grid((N + kMmaCols - 1) / kMmaCols, 1, count);
         cudaFuncSetAttribute(expert_product_mma_kernel<__nv_bfloat16, false, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(mma_shared_bytes(32, false)));
         mlr_launch((expert_product_mma_kernel<__nv_bfloat16, false, 32>), dim3(grid), dim3(256), mma_shared_bytes(32, false), stream, ab, lda, none, 1,
-                   wb, wb, N, K, static_cast<__nv_bfloat16*>(out), ldo, none, none, rows, a_step, out_step);
+                   wb, wb, N, K, static_cast<__nv_bfloat16*>(out), ldo, none, none, rows, a_step, out_step, ExpertGate{0, 0.0f, 0.0f, 0.0f});
     }
     return mlr_launched("batched_product");
 }

@@ -3,7 +3,8 @@
 //
 //   if delta:  h[row] += groupnorm(delta[row] + bias) * w_post      (the sub-layer's result, normed, joins the stream;
 //                                                                   with norm_delta = 0 it joins as it is)
-//   if out:    out[r]  = groupnorm(h[row]) * w_pre                  (the next sub-layer's input)
+//   if out:    out[r]  = groupnorm(h[row]) * w_pre                  (the next sub-layer's input; with bit 1 of `norm_delta`
+//                                                                   set it is h[row] itself: a sub-layer without a norm in front)
 //
 // groupnorm(x): x in `groups` equal consecutive parts, each divided by sqrt(mean(part^2) + eps).
 // groups = 1 is the ordinary RMS norm.  row = rows[r] when an index list is given (the wanted rows
@@ -31,7 +32,8 @@ __device__ __forceinline__ void group_inverse_rms(const float* vals, float* inv,
 template <typename T>
 __global__ void __launch_bounds__(kThreads) group_rmsnorm_kernel(float* h, const float* delta, int ld_delta, const float* bias,
                                                                  const float* w_post, const float* w_pre, T* out, int ld_out,
-                                                                 const int* rows, int width, int groups, float eps, int norm_delta) {
+                                                                 const int* rows, int width, int groups, float eps, int mode) {
+    const int norm_delta = mode & 1, plain_out = mode & 2;
     mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     float* vals = reinterpret_cast<float*>(smem);
@@ -55,10 +57,15 @@ __global__ void __launch_bounds__(kThreads) group_rmsnorm_kernel(float* h, const
         for (int i = threadIdx.x; i < width; i += kThreads) vals[i] = hrow[i];
     }
     if (!out) return;
+    T* o = out + static_cast<size_t>(blockIdx.x) * ld_out;
+    if (plain_out) {           // every thread wrote the values it reads back
+        for (int i = threadIdx.x; i < width; i += kThreads) mlr_store(o, i, vals[i]);
+        mlr_grid_dependents_may_start();
+        return;
+    }
     __syncthreads();
     group_inverse_rms(vals, inv, width, groups, eps);
     __syncthreads();
-    T* o = out + static_cast<size_t>(blockIdx.x) * ld_out;
     for (int i = threadIdx.x; i < width; i += kThreads) {
         const float normed = vals[i] * inv[i / part];
         mlr_store(o, i, w_pre ? normed * w_pre[i] : normed);

@@ -1,2 +1,2 @@
 """Importing this package registers the architectures."""
-from . import gopevik, niridra, qwen3, sopetar  # noqa: F401
+from . import gopevik, niridra, qwen3, sokolorn, sopetar  # noqa: F401

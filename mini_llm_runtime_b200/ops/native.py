@@ -37,6 +37,8 @@ _SIGNATURES = {
         "mlr_gated_bias": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mlr_gated_bias_shaped": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float,
                                   c_void_p],
+        "mlr_activation": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "mlr_softcap": [c_void_p, c_int, c_int, c_float, c_void_p],
     },
     "gemm_f32": {
         "mlr_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -131,7 +133,7 @@ _SIGNATURES = {
     },
     "experts": {
         "mlr_experts_route": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mlr_experts_arrange": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p],
         "mlr_experts_tensor_cores": [c_int, c_longlong],
@@ -139,7 +141,7 @@ _SIGNATURES = {
         "mlr_batched_product_bf16_strided": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "mlr_experts_max_tiles": [c_int, c_int],
         "mlr_experts_product": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
-                                c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                                c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
         "mlr_experts_combine": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
                                 c_longlong, c_int, c_int, c_void_p],
     },

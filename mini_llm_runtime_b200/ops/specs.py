@@ -10,13 +10,15 @@ from __future__ import annotations
 import ctypes
 
 GATES = {None: 0, "sigmoid": 1, "silu": 2, "sigmoid_head": 3}      # "sigmoid_head": one gate value per head, not per value
+QK_NORMS = {None: 0, "head": 1, "whole": 2}                        # a weighted RMS norm of q and k: per head, or over all heads at once
 
 
 class MaskedAttentionSpec(ctypes.Structure):
-    _fields_ = [("freq", ctypes.c_void_p), ("sinks", ctypes.c_void_p), ("slopes", ctypes.c_void_p),
+    _fields_ = [("freq", ctypes.c_void_p), ("sinks", ctypes.c_void_p), ("slopes", ctypes.c_void_p), ("q_weight", ctypes.c_void_p),
+                ("k_weight", ctypes.c_void_p),
                 ("heads", ctypes.c_int32), ("kv_heads", ctypes.c_int32), ("dim", ctypes.c_int32), ("vdim", ctypes.c_int32),
                 ("rot_dims", ctypes.c_int32), ("window", ctypes.c_int32), ("chunk", ctypes.c_int32), ("sink", ctypes.c_int32),
-                ("gate_kind", ctypes.c_int32), ("shared_kv", ctypes.c_int32), ("keep_first", ctypes.c_int32),
+                ("gate_kind", ctypes.c_int32), ("shared_kv", ctypes.c_int32), ("keep_first", ctypes.c_int32), ("qk_norm", ctypes.c_int32),
                 ("scale", ctypes.c_float), ("out_scale", ctypes.c_float), ("softcap", ctypes.c_float)]
 
 

@@ -40,23 +40,31 @@ class TokenEmbedding(Embedding):
 
 
 class LinearHead(Head):
+    """Parameters: vocab_size, width, softcap (default none: with a cap c the logits are c * tanh(logits / c))."""
+
     def __init__(self, spec):
         super().__init__(spec)
         self.vocab = int(spec.params["vocab_size"])
         self.width = int(spec.params["width"])
+        self.softcap = float(spec.params.get("softcap") or 0.0)
         self.weight = None
 
     def weight_specs(self) -> List[WeightSpec]:
         return [WeightSpec(self.spec.weights["weight"], (self.vocab, self.width))]
 
     def kernel_modules(self, dtype) -> List[str]:
-        return F.product_modules(dtype)
+        return F.product_modules(dtype) + (["elementwise"] if self.softcap else [])
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         self.weight = rt.shared_matrix(self.spec.weights["weight"], tensors)
 
     def emit(self, b, x):
-        return b.rt.linear(b, x, self.weight, out_dtype=torch.float32, out=b.logits(self.vocab))
+        out = b.rt.linear(b, x, self.weight, out_dtype=torch.float32, out=b.logits(self.vocab))
+        if self.softcap:
+            if out.ld != self.vocab:
+                raise native.KernelError("the cap on the logits takes rows that lie side by side")
+            b.launch("elementwise", "mlr_softcap", out.ptr, x.rows, self.vocab, self.softcap, b.stream, need="want")
+        return out
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

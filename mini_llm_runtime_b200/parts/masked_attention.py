@@ -29,6 +29,11 @@ Further parameters, all off unless named (with any of the first four the step's 
     slopes      one number per head: score -= slope_h * (query position - key position)
     sink        "learned": the sink's score is a weight per head ("sink" [H]) instead of 0
     gate        "sigmoid_head": one gate value per head ("g" [H, W])
+    qk_norm     a weighted RMS norm of q and k (eps `eps`) before rotation: "head": every head over its own root mean square,
+                times one weight for all heads ("q_norm", "k_norm" [D]); "whole": the whole projection (all heads at once) over
+                its root mean square, times a weight of its size ("q_norm" [H D], "k_norm" [G D])
+    own_kv      False: the layer reads the keys and values that the run named by its `Run.kv_from` cached (as that cache holds
+                them: normed, rotated) and has no "k", "v", "k_norm" and no biases but "q_bias"
 """
 from __future__ import annotations
 
@@ -40,7 +45,7 @@ from ..config.base import ConfigError
 from ..config.registry import register_part
 from ..ops import functions as F
 from ..ops import native
-from ..ops.specs import GATES, MaskedAttentionSpec, address
+from ..ops.specs import GATES, QK_NORMS, MaskedAttentionSpec, address
 from .base import CacheNeed, RunContext, SequenceCore, columns_of
 
 
@@ -64,6 +69,14 @@ class MaskedAttentionMixer(SequenceCore):
         self.keep_first = int(p.get("keep_first") or 0)
         self.softcap = float(p.get("softcap") or 0.0)
         self.slopes = [float(v) for v in p["slopes"]] if p.get("slopes") is not None else None
+        self.qk_norm = p.get("qk_norm")
+        self.own_kv = bool(p.get("own_kv", True))
+        if self.qk_norm not in QK_NORMS:
+            raise ConfigError(f"unknown norm of q and k {self.qk_norm!r}")
+        if self.qk_norm is not None and (self.unit_qk or self.eps <= 0):
+            raise ConfigError("a weighted norm of q and k needs a positive eps and stands instead of the division of heads")
+        if not self.own_kv and (self.unit_v or p.get("value_mix") is not None):
+            raise ConfigError("a layer that reads another layer's keys and values changes no values")
         if self.value_mix not in (None, "first", "later"):
             raise ConfigError(f"unknown value mixing {self.value_mix!r}")
         if self.keep_first and (self.window is None or self.chunk is not None):
@@ -97,7 +110,9 @@ class MaskedAttentionMixer(SequenceCore):
         return CacheNeed(None if self.keep_first else self.window, self.kv_heads, self.dim, self.vdim)
 
     def in_roles(self) -> List[Tuple[str, int]]:
-        roles = [("q", self.heads * self.dim), ("k", self.kv_heads * self.dim), ("v", self.kv_heads * self.vdim)]
+        roles = [("q", self.heads * self.dim)]
+        if self.own_kv:
+            roles += [("k", self.kv_heads * self.dim), ("v", self.kv_heads * self.vdim)]
         if self.gate:
             roles.append(("g", self.heads if self.gate == "sigmoid_head" else self.heads * self.vdim))
         return roles
@@ -106,9 +121,15 @@ class MaskedAttentionMixer(SequenceCore):
         from ..weights.loader import WeightSpec
         w, specs = self.spec.weights, []
         if self.bias:
-            specs += [WeightSpec(w["q_bias"], (self.heads * self.dim,), "vector", ("normal", 0.02)),
-                      WeightSpec(w["k_bias"], (self.kv_heads * self.dim,), "vector", ("normal", 0.02)),
-                      WeightSpec(w["v_bias"], (self.kv_heads * self.vdim,), "vector", ("normal", 0.02))]
+            specs.append(WeightSpec(w["q_bias"], (self.heads * self.dim,), "vector", ("normal", 0.02)))
+            if self.own_kv:
+                specs += [WeightSpec(w["k_bias"], (self.kv_heads * self.dim,), "vector", ("normal", 0.02)),
+                          WeightSpec(w["v_bias"], (self.kv_heads * self.vdim,), "vector", ("normal", 0.02))]
+        if self.qk_norm is not None:
+            whole = self.qk_norm == "whole"
+            specs.append(WeightSpec(w["q_norm"], (self.heads * self.dim if whole else self.dim,), "vector", ("one_plus_normal", 0.05)))
+            if self.own_kv:
+                specs.append(WeightSpec(w["k_norm"], (self.kv_heads * self.dim if whole else self.dim,), "vector", ("one_plus_normal", 0.05)))
         if self.value_mix is not None:
             specs.append(WeightSpec(w["vmix"], (), "vector", ("normal", 0.3)))
         if self.learned_sink:
@@ -117,7 +138,7 @@ class MaskedAttentionMixer(SequenceCore):
 
     @property
     def _prepares(self) -> bool:
-        return self.bias or self.unit_qk or self.unit_v or self.value_mix is not None
+        return self.bias or self.unit_qk or self.unit_v or self.value_mix is not None or self.qk_norm is not None
 
     def core_width(self) -> int:
         return self.heads * self.vdim
@@ -132,12 +153,18 @@ class MaskedAttentionMixer(SequenceCore):
         f32 = lambda t: t.to(device=rt.device, dtype=torch.float32).contiguous()
         self._sinks = f32(rt.vector(tensors[w["sink"]])) if self.learned_sink else None
         self._slopes = torch.tensor(self.slopes, dtype=torch.float32, device=rt.device) if self.slopes is not None else None
-        self._biases = [f32(rt.vector(tensors[w[r]])) for r in ("q_bias", "k_bias", "v_bias")] if self.bias else [None] * 3
+        self._biases = [f32(rt.vector(tensors[w[r]])) if self.bias and (self.own_kv or r == "q_bias") else None
+                        for r in ("q_bias", "k_bias", "v_bias")]
+        self._q_weight = f32(rt.vector(tensors[w["q_norm"]])) if self.qk_norm is not None else None
+        self._k_weight = f32(rt.vector(tensors[w["k_norm"]])) if self.qk_norm is not None and self.own_kv else None
         self._lambda = float(tensors[w["vmix"]].float().item()) if self.value_mix == "later" else 0.0
         self.desc = MaskedAttentionSpec(
             freq=freq.data_ptr() if freq is not None and freq.numel() else None,
             sinks=self._sinks.data_ptr() if self._sinks is not None else None,
-            slopes=self._slopes.data_ptr() if self._slopes is not None else None, heads=self.heads, kv_heads=self.kv_heads, dim=self.dim,
+            slopes=self._slopes.data_ptr() if self._slopes is not None else None,
+            q_weight=self._q_weight.data_ptr() if self._q_weight is not None else None,
+            k_weight=self._k_weight.data_ptr() if self._k_weight is not None else None, qk_norm=QK_NORMS[self.qk_norm],
+            heads=self.heads, kv_heads=self.kv_heads, dim=self.dim,
             vdim=self.vdim, rot_dims=self.position.dims if self.position is not None else 0, window=self.window or 0,
             chunk=self.chunk or 0, sink=int(self.sink), gate_kind=GATES[self.gate], keep_first=self.keep_first, scale=self.scale,
             out_scale=float(out_scale), softcap=self.softcap)
@@ -146,13 +173,19 @@ class MaskedAttentionMixer(SequenceCore):
         if run.cache is None or run.cache.dtype is not proj.dtype:
             raise native.KernelError("masked attention: the cache must have the activations' precision")
         at = self.in_columns()
-        k = columns_of(proj, at["k"], self.kv_heads * self.dim)
-        v = columns_of(proj, at["v"], self.kv_heads * self.vdim)
+        if self.own_kv != bool(run.write_cache):
+            raise native.KernelError("masked attention: a layer writes the cache exactly when it makes keys and values of its own")
+        k = columns_of(proj, at["k"], self.kv_heads * self.dim) if self.own_kv else None
+        v = columns_of(proj, at["v"], self.kv_heads * self.vdim) if self.own_kv else None
         gate = columns_of(proj, at["g"], self.heads if self.gate == "sigmoid_head" else self.heads * self.vdim) if self.gate else None
         table, stride = b.table(run.group), b.table_stride(run.group)
-        if self._prepares:
-            if not run.write_cache:
-                raise native.KernelError("masked attention: a layer that prepares its keys and values writes its own cache")
+        if self._prepares and not self.own_kv:
+            # Queries only: biases and the norm in place; the attention kernels rotate them as they load them.
+            b.launch("attention_masked", "mlr_qkv_prepare_cache", address(self.desc), proj.ptr, proj.ld, None, 0, None, 0, proj.is_bf16,
+                     self._biases[0].data_ptr() if self._biases[0] is not None else None, None, None, int(self.unit_qk), 0, self.eps,
+                     None, 0, 0, 0.0, None, 0, b.meta("positions"), b.meta("segment_of_row"), None, 0, b.page_size, proj.rows,
+                     b.status, b.stream)
+        elif self._prepares:
             first = None
             if self.value_mix is not None:
                 first = b.kept(("value_mix", self.kv_heads, self.vdim), proj.rows, self.kv_heads * self.vdim, torch.float32)

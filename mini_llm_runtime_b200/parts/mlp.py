@@ -104,3 +104,39 @@ class GatedBiasFeedForward(FeedForward):
 
 
 register_part("feed_forward", "gated_bias", GatedBiasFeedForward)
+
+
+class PlainFeedForward(FeedForward):
+    """Feed-forward without a gate: `down(act(up(x)))`, no biases; act is the square of relu ("relu2"), the tanh form of
+    GELU ("gelu_tanh") or SiLU ("silu"), applied by a row-wise kernel between the two products.
+    Parameters: hidden_size, intermediate_size, activation.  Weights: "up" [I, width], "down" [width, I]."""
+    ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.activation = self.ACTIVATIONS[spec.params["activation"]]
+        self.w_up = self.w_down = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        w = self.spec.weights
+        return [WeightSpec(w["up"], (self.inter, self.width)), WeightSpec(w["down"], (self.width, self.inter))]
+
+    def kernel_modules(self, dtype) -> List[str]:
+        return ["elementwise"] + F.product_modules(dtype)
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
+        w = self.spec.weights
+        self.w_up, self.w_down = rt.matrix(tensors[w["up"]]), rt.matrix(tensors[w["down"]])
+
+    def emit(self, b, x):
+        rt = b.rt
+        up = rt.linear(b, x, self.w_up, activation=True)
+        b.launch("elementwise", "mlr_activation", up.ptr, up.ld, up.ptr, up.ld, up.is_bf16, x.rows, self.inter, self.activation, b.stream)
+        if b.residual is not None:
+            return rt.linear_delta(b, up, self.w_down, into=b.residual)
+        return rt.linear(b, up, self.w_down, out_dtype=torch.float32)      # a block whose norm stands behind wants the plain result
+
+
+register_part("feed_forward", "plain", PlainFeedForward)

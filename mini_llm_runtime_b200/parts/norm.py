@@ -69,26 +69,32 @@ class GroupRmsNorm(Norm):
 
     Besides the interface of every norm (`emit`: add a pending contribution as it is, then norm) it can
     stand BEHIND a sub-layer: `emit_residual` adds norm(contribution [+ bias]) * weight into the stream,
-    and in the same launch applies the norm that reads the stream next (`then`), if one is named.
-    Parameters: width, groups, eps.  Weights: "weight" [width]."""
+    and in the same launch applies the norm that reads the stream next (`then`), if one is named: a grouped norm of the
+    same shape, or no norm at all (`identity`: the sub-layers of such a model read the stream as it is).
+    With `offset` the stored weight is the distance from that number: the norm multiplies by offset + weight.
+    Parameters: width, groups, eps, offset (default 0).  Weights: "weight" [width]."""
 
     def __init__(self, spec):
         super().__init__(spec)
         self.width = int(spec.params["width"])
         self.groups = int(spec.params.get("groups", 1))
         self.eps = float(spec.params["eps"])
+        self.offset = float(spec.params.get("offset") or 0.0)
         if self.groups < 1 or self.width % self.groups:
             raise ValueError(f"a norm over {self.width} values cannot have {self.groups} equal groups")
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.spec.weights["weight"], (self.width,), "vector", ("one_plus_normal", 0.01))]
+        init = ("normal", 0.05) if self.offset else ("one_plus_normal", 0.01)
+        return [WeightSpec(self.spec.weights["weight"], (self.width,), "vector", init)]
 
     def kernel_modules(self, dtype) -> List[str]:
         return ["norm_grouped"]
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         self.weight = rt.vector(tensors[self.spec.weights["weight"]]).float()
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()       # float32: 1 + w keeps what bfloat16 would drop
 
     def foldable(self):
         """The block before may apply this norm in the launch that ends it (`emit_residual(then=...)`) and leave the
@@ -112,27 +118,76 @@ class GroupRmsNorm(Norm):
         return out
 
     def same_shape(self, other) -> bool:
+        if isinstance(other, IdentityNorm):
+            return other.width == self.width
         return isinstance(other, GroupRmsNorm) and (other.width, other.groups, other.eps) == (self.width, self.groups, self.eps)
 
-    def emit_residual(self, b, h, delta, then: Optional["GroupRmsNorm"] = None):
+    def emit_residual(self, b, h, delta, then: Optional[Norm] = None):
         """h += norm(delta + its bias) * weight; returns then(h) in the activation dtype, or None."""
         if delta.slices:
             raise native.KernelError("the grouped norm takes a plain [rows, width] contribution")
+        plain = isinstance(then, IdentityNorm)
+        if plain and then.reads_stream(b, h):
+            then = None                 # the reader takes the float32 stream itself: nothing to write for it
         if then is not None and not self.same_shape(then):
             out = None
         else:
             out = b.temp(h.rows, self.width, b.rt.dtype) if then is not None else None
         bias = getattr(delta, "bias", None)
         b.launch("norm_grouped", "mlr_group_rmsnorm", h.ptr, delta.ptr, delta.ld, bias.data_ptr() if bias is not None else None,
-                 self.weight.data_ptr(), then.weight.data_ptr() if out is not None else None,
+                 self.weight.data_ptr(), then.weight.data_ptr() if out is not None and not plain else None,
                  out.ptr if out is not None else None, out.ld if out is not None else 0, int(b.rt.is_bf16), None, h.rows,
-                 self.width, self.groups, self.eps, 1, b.stream)
+                 self.width, self.groups, self.eps, 1 | (2 if plain else 0), b.stream)
+        if plain and then is None:
+            return h
         if then is not None and out is None:
             return then.emit(b, h, None)
         return out
 
 
 register_part("norm", "group_rmsnorm", GroupRmsNorm)
+
+
+class IdentityNorm(Norm):
+    """No norm: the reader takes the residual stream as it is, in the activation dtype.  It stands where a block expects a
+    norm in front of a sub-layer in designs whose norms stand behind their sub-layers only.  On the 32-bit path the result
+    IS the stream (no launch, no copy); in bfloat16 it is the stream's rounding, written by the launch that last added into
+    the stream (`GroupRmsNorm.emit_residual(then=...)`) or by a launch of its own.  Parameters: width.  No weights."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width = int(spec.params["width"])
+        self.weight = None
+
+    def kernel_modules(self, dtype) -> List[str]:
+        return ["norm_grouped"]
+
+    def foldable(self):
+        return ("group_rms", self)
+
+    def reads_stream(self, b, h) -> bool:
+        return b.rt.dtype is torch.float32 and h.dtype is torch.float32 and h.ld == h.width == self.width
+
+    def emit(self, b, h, delta, wanted_only: bool = False):
+        if delta is not None and (delta.slices or wanted_only or getattr(delta, "norm", None) is not None):
+            raise native.KernelError("this part adds a plain [rows, width] contribution for all rows only")
+        prepared, b.prepared = b.prepared, None
+        if (delta is None and not wanted_only and isinstance(prepared, dict) and prepared.get("group_rms") is self
+                and prepared.get("stream") is h):
+            return prepared["out"]          # the launch that ended the block before has written the copy already
+        if delta is None and not wanted_only and self.reads_stream(b, h):
+            return h
+        count = b.want if wanted_only else h.rows
+        out = b.temp(count, self.width, b.rt.dtype)
+        bias = getattr(delta, "bias", None) if delta is not None else None
+        b.launch("norm_grouped", "mlr_group_rmsnorm", h.ptr, delta.ptr if delta is not None else None,
+                 delta.ld if delta is not None else 0, bias.data_ptr() if bias is not None else None, None, None, out.ptr, out.ld,
+                 out.is_bf16, b.meta("want_rows") if wanted_only else None, count, self.width, 1, 0.0, 2, b.stream,
+                 need="want" if wanted_only else None)
+        return out
+
+
+register_part("norm", "identity", IdentityNorm)
 
 
 class LayerNorm(Norm):

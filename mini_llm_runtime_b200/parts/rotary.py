@@ -50,6 +50,18 @@ class Rope(PositionEncoding):
 register_part("position", "rope", Rope)
 
 
+def scaled_frequencies(freq: np.ndarray, factor: float, low: float, high: float, original: float) -> np.ndarray:
+    """Frequencies whose long wavelengths are slowed down, as a model does that was trained on `original` positions and
+    is to read `factor` times as many: with the wavelength l = 2 pi / f, a frequency stays where l < original / high,
+    becomes f / factor where l > original / low, and in between is the blend (1 - s) f / factor + s f with
+    s = (original / l - low) / (high - low).  float64 in, float64 out."""
+    freq = np.asarray(freq, dtype=np.float64)
+    length = 2.0 * np.pi / freq
+    s = (original / length - low) / (high - low)
+    blend = (1.0 - s) * freq / factor + s * freq
+    return np.where(length < original / high, freq, np.where(length > original / low, freq / factor, blend))
+
+
 class RotaryFrequencies(PositionEncoding):
     """Rotation given as its frequencies only: `freq_i = base^(-2i/dims) / factor`, i < dims/2.  The kernels
     that use it compute `position * freq_i` and its cosine and sine in float32 themselves, so no table
@@ -57,7 +69,8 @@ class RotaryFrequencies(PositionEncoding):
     values of a head are rotated; a mixer's heads may be wider.  Value i turns with value i + dims/2, or, with
     `interleaved`, value 2i with value 2i + 1: (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = position * freq_i
     (a mixer's kernels must know that layout; those that do not refuse it).
-    Parameters: base, dims, factor (default 1), interleaved (default False).  No weights."""
+    With `scaling` = {factor, low, high, original} only long wavelengths are slowed down (`scaled_frequencies`).
+    Parameters: base, dims, factor (default 1), interleaved (default False), scaling (default None).  No weights."""
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -67,11 +80,18 @@ class RotaryFrequencies(PositionEncoding):
         self.interleaved = bool(spec.params.get("interleaved", False))
         if self.dims < 0 or self.dims % 2 or self.base <= 0 or self.factor <= 0:
             raise ValueError(f"a rotation of {self.dims} values with base {self.base} and factor {self.factor} is not defined")
+        scaling = spec.params.get("scaling")
+        self.scaling = {k: float(scaling[k]) for k in ("factor", "low", "high", "original")} if scaling else None
+        if self.scaling is not None and not (self.scaling["high"] > self.scaling["low"] and self.scaling["factor"] > 0
+                                             and self.scaling["original"] > 0):
+            raise ValueError(f"a frequency scaling {self.scaling} is not defined")
         self._freq: Optional[torch.Tensor] = None
 
     def bind(self, tensors, rt) -> None:
         i = np.arange(self.dims // 2, dtype=np.float64)
         freq = np.power(self.base, -2.0 * i / max(self.dims, 1)) / self.factor
+        if self.scaling is not None:
+            freq = scaled_frequencies(freq, **self.scaling)
         self._freq = torch.from_numpy(freq.astype(np.float32)).to(rt.device)
 
     def frequencies(self) -> torch.Tensor:

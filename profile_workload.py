@@ -5,7 +5,7 @@ Qwen3-8B layer sizes with few layers, bracketed by cudaProfilerStart/Stop.
     python profile_workload.py prefill [--layers 2] [--tokens 2048] [--mma-sync-attention]
     python profile_workload.py attention [--page-size 64]
     python profile_workload.py products  [--tokens 2048]
-    python profile_workload.py decode|prefill --design gopevik|niridra|sopetar [--layers 4] [--context 2048]
+    python profile_workload.py decode|prefill --design gopevik|niridra|sopetar|sokolorn [--layers 4] [--context 2048]
 
 `attention` times the two bfloat16 attention kernels alone (CUDA events, no model) over a
 range of prompt lengths, contexts, batch sizes and head sizes and prints two tables.
@@ -60,8 +60,8 @@ def main() -> int:
                     help="up to how many rows a product takes the CUDA-core pass over the weights (default: the runtime's setting)")
     ap.add_argument("--mma-sync-attention", action="store_true",
                     help="prompt attention on the mma.sync kernel instead of the tcgen05 one")
-    ap.add_argument("--design", default="qwen3", choices=["qwen3", "gopevik", "niridra", "sopetar"],
-                    help="gopevik, niridra, sopetar: the design at the layer sizes of `bench.py --compare <design>` (width 2048; decode and prefill)")
+    ap.add_argument("--design", default="qwen3", choices=["qwen3", "gopevik", "niridra", "sopetar", "sokolorn"],
+                    help="gopevik, niridra, sopetar, sokolorn: the design at the layer sizes of `bench.py --compare <design>` (width 2048; decode and prefill)")
     args = ap.parse_args()
 
     if args.mode == "attention":

@@ -210,7 +210,7 @@ def test_router_kernel(dtype, experts, groups, keep, top, shared):
     counts = torch.zeros(experts, dtype=torch.int32, device=dev)
     _call("experts", "mlr_experts_route", x.data_ptr(), x.stride(0), native.is_bf16(x), router.data_ptr(), correction.data_ptr(), rows, width,
           experts, groups, keep, top, int(shared), chosen.data_ptr(), weights.data_ptr(), place.data_ptr(), counts.data_ptr(),
-          gate.data_ptr() if shared else None, native.stream())
+          gate.data_ptr() if shared else None, 0, native.stream())
     xd = x.double().cpu()
     want_chosen, want_weights = plain.route(xd, router[:experts].double().cpu(), correction.double().cpu(), top, groups, keep)
     assert torch.equal(chosen.cpu().long(), want_chosen)
