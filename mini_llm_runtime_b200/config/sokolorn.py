@@ -4,8 +4,8 @@
      "layers": [{"type": "attention" | "attention_2", "mixer": {...}, "mlp": {...} | null}, ...]}
 
 An "attention" mixer has heads, kv_heads, dim, vdim, scale and optionally mask.size (a sliding window); an "attention_2"
-mixer has heads, kv_heads, dim, vdim, scale, optionally rot = {base, dims, optionally scaling = {factor, low, high, original}}
-and optionally kv_from (the index of an earlier layer whose cached keys and values it reads).  A feed-forward is
+mixer has heads, kv_heads, dim, vdim, scale and optionally rot = {base, dims, optionally scaling = {factor, low, high, original}}.
+Either may name kv_from: the index of an earlier layer of its type whose cached keys and values it reads.  A feed-forward is
 {"kind": "dense", "ff"} or {"kind": "moe", "expert": {ff, limit}, "router": {experts, top}, optionally "shared": {ff, limit}}.
 Every size and constant comes from the file; a missing required key is an error, and what the file leaves out (a window, a
 rotation, its scaling, a shared expert, a cap on the logits, a feed-forward) does not exist.  The design names no largest
@@ -61,7 +61,7 @@ class SokolornMixer:
     scale: float
     window: Optional[int] = None                # "attention"
     rot: Optional[ScaledRotation] = None        # "attention_2"
-    kv_from: Optional[int] = None               # "attention_2"
+    kv_from: Optional[int] = None               # an earlier layer of the same type whose cached keys and values this one reads
 
 
 @dataclass(frozen=True)
@@ -134,24 +134,23 @@ class SokolornConfig:
             if kind == "attention":
                 mask = m.get("mask")
                 window = _integer(mask, "size", mw + "mask.") if mask is not None and mask.get("size") is not None else None
-                for key in ("rot", "kv_from"):
-                    if m.get(key) is not None:
-                        raise ConfigError(f"config.json key {mw}{key!r} belongs to the mixer 'attention_2'")
+                if m.get("rot") is not None:
+                    raise ConfigError(f"config.json key {mw}'rot' belongs to the mixer 'attention_2'")
             else:
                 rot = ScaledRotation.from_dict(m.get("rot"), mw + "rot.", dim)
                 if m.get("mask") is not None:
                     raise ConfigError(f"config.json key {mw}'mask' belongs to the mixer 'attention'")
-                kv_from = m.get("kv_from")
-                if kv_from is not None and (isinstance(kv_from, bool) or not isinstance(kv_from, int) or not 0 <= kv_from < i):
-                    raise ConfigError(f"config.json key {mw}'kv_from' = {kv_from!r} must be the index of an earlier layer")
+            kv_from = m.get("kv_from")
+            if kv_from is not None and (isinstance(kv_from, bool) or not isinstance(kv_from, int) or not 0 <= kv_from < i):
+                raise ConfigError(f"config.json key {mw}'kv_from' = {kv_from!r} must be the index of an earlier layer")
             mixer = SokolornMixer(heads, kv_heads, dim, _integer(m, "vdim", mw), _number(m, "scale", mw), window, rot, kv_from)
             if kv_from is not None:
                 source = layers[kv_from]
                 if source.type != kind or source.mixer.kv_from is not None:
                     raise ConfigError(f"config.json key {mw}'kv_from' = {kv_from}: that layer is no '{kind}' layer with keys and values of its own")
                 a, b = source.mixer, mixer
-                if (a.kv_heads, a.dim, a.vdim, a.rot) != (b.kv_heads, b.dim, b.vdim, b.rot):
-                    raise ConfigError(f"config.json key {mw}'kv_from' = {kv_from}: key/value heads, sizes and rotation of the two layers differ")
+                if (a.kv_heads, a.dim, a.vdim, a.rot, a.window) != (b.kv_heads, b.dim, b.vdim, b.rot, b.window):
+                    raise ConfigError(f"config.json key {mw}'kv_from' = {kv_from}: key/value heads, sizes, rotation or window of the two layers differ")
             layers.append(SokolornLayer(kind, mixer, cls._mlp(layer.get("mlp"), where + "mlp.")))
         cap = raw.get("logit_softcap")
         eos = raw.get("eos_token_id", ())

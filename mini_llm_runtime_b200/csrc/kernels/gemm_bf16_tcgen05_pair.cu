@@ -37,7 +37,7 @@ constexpr int kOperandBytes = kRows * kTileK * 2;
 constexpr int kStageBytes = 2 * kOperandBytes;          // per block
 constexpr int kStages = 7;
 constexpr int kTmemColumns = 2 * kTileN;                // two accumulators
-enum Epilogue : int { kStoreBf16 = 0, kStoreF32 = 1, kAddF32 = 2, kSiluGateBf16 = 3 };
+enum Epilogue : int { kStoreBf16 = 0, kStoreF32 = 1, kAddF32 = 2, kSiluGateBf16 = 3, kSquaredReluBf16 = 4 };
 
 // dst[0..3] += (a, b, c, d), done by the memory system: the thread does not wait for the old
 // values.  Every element is added to by exactly one thread, once, so the result does not
@@ -195,7 +195,14 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_pair_kernel(const __gri
                     tmem_load16(row_base + c, r);
                     if (p >= P) continue;
                     const bool whole = q0 + c + 16 <= Q && (ldo & 7) == 0;
-                    if (epilogue == kStoreBf16) {
+                    if (epilogue == kSquaredReluBf16) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float v = fmaxf(__uint_as_float(r[j]), 0.0f);
+                            r[j] = __float_as_uint(v * v);
+                        }
+                    }
+                    if (epilogue == kStoreBf16 || epilogue == kSquaredReluBf16) {
                         __nv_bfloat16* dst_row = static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(p) * ldo + q0 + c;
                         if (whole) {
                             uint32_t w[8];
@@ -270,10 +277,10 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 // out[p, q] = sum_k X[p, k] W[q, k] for X [P, K] (row stride ldx) and W [Q, K] (row stride ldw),
 // bfloat16.  epilogue: 0 stores bfloat16, 1 stores float32, 2 adds into float32 `out`, 3 takes
 // W as 128 gate rows alternating with their 128 "up" rows (Q a multiple of 256) and stores
-// bfloat16 silu(gate) * up at out[p, Q / 2 columns].  Row stride of out: ldo elements.
+// bfloat16 silu(gate) * up at out[p, Q / 2 columns], 4 stores bfloat16 relu(x)^2.  Row stride of out: ldo elements.
 MLR_API int mlr_gemm_bf16_tcgen05_pair(const void* X, long long ldx, int P, const void* W, long long ldw, int Q, int K, void* out,
                                        long long ldo, int epilogue, int* status, cudaStream_t stream) {
-    MLR_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm_bf16_tcgen05_pair: epilogue must be 0..3, got %d", epilogue);
+    MLR_REQUIRE(epilogue >= 0 && epilogue <= 4, "gemm_bf16_tcgen05_pair: epilogue must be 0..4, got %d", epilogue);
     MLR_REQUIRE(P >= 1 && Q >= 1 && K >= 8, "gemm_bf16_tcgen05_pair: bad sizes P=%d Q=%d K=%d", P, Q, K);
     MLR_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldx >= K && ldw >= K,
                 "gemm_bf16_tcgen05_pair: K and the operand row strides must be multiples of 8 elements (16 bytes), got K=%d", K);

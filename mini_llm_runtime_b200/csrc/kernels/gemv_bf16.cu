@@ -68,7 +68,7 @@ constexpr int kMaxRows = 8;
 constexpr int kPartialBytes = kConsumerWarps * kUnitRows * kMaxRows * 4;        // one buffer of the warps' partial sums
 constexpr long long kWaitLimitCycles = 4000000000LL;      // about two seconds
 
-enum Mode : int { kStoreBf16 = 0, kStoreF32 = 1, kAddF32 = 2, kSiluGateBf16 = 3 };
+enum Mode : int { kStoreBf16 = 0, kStoreF32 = 1, kAddF32 = 2, kSiluGateBf16 = 3, kSquaredReluBf16 = 4 };
 
 struct Link {
     const __nv_bfloat16* W;
@@ -437,6 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
                             const int row = unit * kUnitRows + r;
                             if (row < l.N) {
                                 if (l.mode == kStoreBf16) static_cast<__nv_bfloat16*>(l.out)[at + row] = __float2bfloat16_rn(y);
+                                else if (l.mode == kSquaredReluBf16) static_cast<__nv_bfloat16*>(l.out)[at + row] = __float2bfloat16_rn(fmaxf(y, 0.0f) * fmaxf(y, 0.0f));
                                 else if (l.mode == kStoreF32) static_cast<float*>(l.out)[at + row] = y;
                                 else {
                                     float* cell = static_cast<float*>(l.out) + at + row;
@@ -515,7 +516,7 @@ int parts_of(int M, int K, int mode, int norm, int& part_width) {
 
 int check_link(const Link& l) {
     MLR_REQUIRE(l.N >= 1 && l.K >= 8 && l.K % 8 == 0, "gemv_bf16: bad sizes N=%d K=%d (K must be a multiple of 8)", l.N, l.K);
-    MLR_REQUIRE(l.mode >= kStoreBf16 && l.mode <= kSiluGateBf16, "gemv_bf16: unknown mode %d", l.mode);
+    MLR_REQUIRE(l.mode >= kStoreBf16 && l.mode <= kSquaredReluBf16, "gemv_bf16: unknown mode %d", l.mode);
     MLR_REQUIRE(l.mode != kSiluGateBf16 || l.N % (2 * kGateBlock) == 0,
                 "gemv_bf16: a stacked gate/up matrix has a multiple of 256 rows, got %d", l.N);
     MLR_REQUIRE(l.ldw % 8 == 0 && reinterpret_cast<uintptr_t>(l.W) % 16 == 0, "gemv_bf16: the weight rows must be 16-byte aligned");
@@ -604,7 +605,7 @@ MLR_API int mlr_gemv_bf16_parts(int M, int K) {
 // bfloat16 or float32, `eps`) of its row row_index[r] (r when row_index is null), rounded to bfloat16.
 // mode 0: out bfloat16 [M, N]; 1: out float32 [M, N]; 2: out float32 [M, N] += the product; 3: W is a
 // stacked gate/up matrix (blocks of 128 gate rows, each followed by its 128 "up" rows; N a multiple of
-// 256) and out is bfloat16 [M, N / 2] = silu(gate) * up.  `ldo`: elements between rows of out.  `status`: a
+// 256) and out is bfloat16 [M, N / 2] = silu(gate) * up; 4: out bfloat16 [M, N] = relu(product)^2.  `ldo`: elements between rows of out.  `status`: a
 // device word in which a wait that ran out sets MLR_STATUS_TIMEOUT.
 MLR_API int mlr_gemv_bf16(const void* W, long long ldw, int N, int K, const void* x, long long ldx, int norm,
                           const void* norm_weight, int norm_weight_bf16, float eps, const int* row_index, int M, void* out,

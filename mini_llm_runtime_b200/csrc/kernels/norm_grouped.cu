@@ -9,7 +9,8 @@
 // groupnorm(x): x in `groups` equal consecutive parts, each divided by sqrt(mean(part^2) + eps).
 // groups = 1 is the ordinary RMS norm.  row = rows[r] when an index list is given (the wanted rows
 // before the head), else r.  One block per row; the row is staged in shared memory, each warp
-// sums whole groups in a fixed order, so a row's result depends on nothing but the row.
+// sums whole groups in a fixed order (a single group is summed by all warps, their sums added in
+// order), so a row's result depends on nothing but the row.
 // All arithmetic is float32; `out` is float32 or bfloat16; weights and the bias are float32.
 #include "common.cuh"
 
@@ -17,9 +18,24 @@ namespace {
 
 constexpr int kThreads = 256;
 
+// Leaves inv[g] for every group; the caller meets at a barrier before reading them.  With ONE group (the ordinary RMS norm)
+// all warps share the sum: every thread adds its columns, then the warps' sums are added in order (`inv[1 ..]` is their room).
 __device__ __forceinline__ void group_inverse_rms(const float* vals, float* inv, int width, int groups, float eps) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int part = width / groups;
+    if (groups == 1) {
+        float sum = 0.0f;
+        for (int i = threadIdx.x; i < width; i += kThreads) sum = fmaf(vals[i], vals[i], sum);
+        sum = mlr_warp_sum(sum);
+        if (lane == 0) inv[1 + warp] = sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float total = 0.0f;
+            for (int w = 0; w < warps; ++w) total += inv[1 + w];
+            inv[0] = 1.0f / sqrtf(total / static_cast<float>(width) + eps);
+        }
+        return;
+    }
     for (int g = warp; g < groups; g += warps) {
         const float* x = vals + static_cast<size_t>(g) * part;
         float sum = 0.0f;
@@ -85,7 +101,7 @@ MLR_API int mlr_group_rmsnorm(float* h, const float* delta, int ld_delta, const 
     MLR_REQUIRE(!delta || (ld_delta >= width && !rows), "group_rmsnorm: a contribution is added for all rows, with a row stride >= width");
     MLR_REQUIRE(!out || ld_out >= width, "group_rmsnorm: the output's row stride is smaller than the width");
     if (count == 0) return 0;
-    const size_t shared = sizeof(float) * (static_cast<size_t>(width) + groups);
+    const size_t shared = sizeof(float) * (static_cast<size_t>(width) + groups + kThreads / 32);
     MLR_REQUIRE(shared <= 200 * 1024, "group_rmsnorm: a row of %d values does not fit shared memory", width);
     if (shared > 48 * 1024) {
         cudaFuncSetAttribute(group_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));

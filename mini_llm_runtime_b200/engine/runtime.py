@@ -398,6 +398,27 @@ class Runtime:
                 return None
         return self.linear(b, x, w, out_dtype=torch.float32)
 
+    # ---- a product whose result goes through an activation without a gate
+    ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+    def activated_linear(self, b, x: Buf, w: torch.Tensor, activation: str) -> Buf:
+        """act(x W^T) in the activation dtype.  The square of relu lives in the epilogue of the few-row kernel (decode) and of
+        the two-SM tcgen05 kernel (prompt portions of `pair_rows` rows and more, with enough tiles); otherwise the product is
+        followed by a row-wise kernel, in place."""
+        N = w.shape[0]
+        out = b.temp(x.rows, N, self.dtype)
+        if activation == "relu2" and self.dtype is torch.bfloat16:
+            if self._gemv(b, x, w):
+                self._gemv_launch(b, x, w, out, "relu2")
+                return out
+            x = self.materialize(b, x)
+            if self._pair(b, x, w, gated=True):
+                self._pair_launch(b, x, w, out, "relu2")
+                return out
+        out = self.linear(b, x, w, activation=True, out=out)
+        b.launch("elementwise", "mlr_activation", out.ptr, out.ld, out.ptr, out.ld, out.is_bf16, x.rows, N, self.ACTIVATIONS[activation], b.stream)
+        return out
+
     # ---- the gated pair of matrices of a feed-forward
     def stack_gate_up(self, w_gate: torch.Tensor, w_up: torch.Tensor):
         """The two [I, K] matrices as the one operand `gated_linear` takes, and the width I' of

@@ -268,7 +268,7 @@ def finite_check(t: torch.Tensor, flag: torch.Tensor) -> None:
     call("weights", "mlr_finite_check", ptr(t), is_bf16(t), t.numel(), ptr(flag), stream())
 
 
-GEMV_MODES = {"bf16": 0, "f32": 1, "add_f32": 2, "silu_gate": 3}
+GEMV_MODES = {"bf16": 0, "f32": 1, "add_f32": 2, "silu_gate": 3, "relu2": 4}
 
 
 def _gemv_operands(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, mode: str, x_dtype: torch.dtype) -> None:
@@ -374,7 +374,7 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, statu
              ldo, f32, 0, tile_q, splits, split_stride, 2, ptr(status), stream())
 
 
-PAIR_EPILOGUES = {"bf16": 0, "f32": 1, "add_f32": 2, "silu_gate": 3}
+PAIR_EPILOGUES = {"bf16": 0, "f32": 1, "add_f32": 2, "silu_gate": 3, "relu2": 4}
 
 
 def gemm_bf16_tcgen05_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor, epilogue: str) -> None:

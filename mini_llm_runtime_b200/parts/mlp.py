@@ -108,7 +108,8 @@ register_part("feed_forward", "gated_bias", GatedBiasFeedForward)
 
 class PlainFeedForward(FeedForward):
     """Feed-forward without a gate: `down(act(up(x)))`, no biases; act is the square of relu ("relu2"), the tanh form of
-    GELU ("gelu_tanh") or SiLU ("silu"), applied by a row-wise kernel between the two products.
+    GELU ("gelu_tanh") or SiLU ("silu"), applied in the first product's epilogue where its kernel has one
+    (`Runtime.activated_linear`) and by a row-wise kernel between the two products otherwise.
     Parameters: hidden_size, intermediate_size, activation.  Weights: "up" [I, width], "down" [width, I]."""
     ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
 
@@ -132,8 +133,7 @@ class PlainFeedForward(FeedForward):
 
     def emit(self, b, x):
         rt = b.rt
-        up = rt.linear(b, x, self.w_up, activation=True)
-        b.launch("elementwise", "mlr_activation", up.ptr, up.ld, up.ptr, up.ld, up.is_bf16, x.rows, self.inter, self.activation, b.stream)
+        up = rt.activated_linear(b, x, self.w_up, self.spec.params["activation"])
         if b.residual is not None:
             return rt.linear_delta(b, up, self.w_down, into=b.residual)
         return rt.linear(b, up, self.w_down, out_dtype=torch.float32)      # a block whose norm stands behind wants the plain result

@@ -3,7 +3,7 @@ width, vocabulary, layer order (starting with either mixer, one kind only), quer
 of their own in both mixers, key and value sizes that differ, windows of 1, of a few tokens, of more than a tile of keys,
 larger than every prompt, and none; rotation of a whole head, of a part of it, and none; frequency scaling whose three
 zones (kept, blended, slowed) all occur, and none; layers that read the keys and values of the layer before them and of a
-layer further back, two readers of one layer; dense and routed feed-forwards and none; 1 of n, several of n and all of n
+layer further back, two readers of one layer, a windowed reader; dense and routed feed-forwards and none; 1 of n, several of n and all of n
 experts, with and without a shared expert, limits that clamp often and never; with and without a cap on the logits."""
 from __future__ import annotations
 
@@ -14,10 +14,12 @@ from typing import Dict
 import torch
 
 
-def _windowed(heads, kv_heads, dim, vdim, scale, mlp, window=None):
+def _windowed(heads, kv_heads, dim, vdim, scale, mlp, window=None, kv_from=None):
     mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
     if window is not None:
         mixer["mask"] = {"size": window}
+    if kv_from is not None:
+        mixer["kv_from"] = kv_from
     return {"type": "attention", "mixer": mixer, "mlp": mlp}
 
 
@@ -93,7 +95,8 @@ SMALL_C = {
 # One kind of mixer only, each in a model of its own.
 ONLY_WINDOWED = {
     "architecture": "Sokolorn", "vocab": 61, "width": 32, "norm": {"eps": 1e-5}, "logit_softcap": 5.0,
-    "layers": [_windowed(2, 1, 16, 16, 0.3, _dense(16), window=6), _windowed(4, 1, 8, 16, 0.5, None, window=3)],
+    "layers": [_windowed(2, 1, 16, 16, 0.3, _dense(16), window=6), _windowed(4, 1, 8, 16, 0.5, None, window=3),
+               _windowed(4, 1, 16, 16, 0.4, _dense(24), window=6, kv_from=0)],
 }
 ONLY_ROTARY = {
     "architecture": "Sokolorn", "vocab": 61, "width": 32, "norm": {"eps": 1e-5},
@@ -140,7 +143,8 @@ def random_weights(config: dict, seed: int) -> Dict[str, torch.Tensor]:
         matrix(p + "mix.o", W, H * Dv)
         if layer["type"] == "attention":
             vector(p + "mix.q.norm", H * D, 1.0, 0.2)
-            vector(p + "mix.k.norm", G * D, 1.0, 0.2)
+            if own:
+                vector(p + "mix.k.norm", G * D, 1.0, 0.2)
             vector(p + "mix.sink", H, 0.5, 1.0)
             matrix(p + "mix.g", H, W, 2.0)
         else:
