@@ -38,6 +38,10 @@ struct MaskedAttentionSpec {
     int shared_kv;         // 1: a token's value is the first vdim values of its key (vdim <= dim; one vector per token is cached and a page holds keys only)
     int keep_first;        // with a window: the first keep_first positions stay visible
     int qk_norm;           // 0 none; 1 every head of q and k over its root mean square, times a weight; 2 the WHOLE projection (all heads) likewise
+    int dense_cache;       // 1: `mlr_qkv_prepare_cache` serves the kernels of the plain causal attention (attention_bf16, attention_tcgen05,
+                           // attention_generic) instead of this file's: it also rotates the queries in place, and writes the cache as those
+                           // kernels read it ([page][K | V][kv_head][token][dim] with dim = vdim, bfloat16 rows of 64, 128 or 256 values with
+                           // their 16-byte chunks swizzled by the position: `mlr_cache_col`)
     float scale, out_scale;
     float softcap;         // > 0: score <- softcap * tanh(score / softcap)
 };
@@ -148,6 +152,7 @@ __global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int l
                static_cast<size_t>(position % page_size) * s.vdim;
     const int half = s.rot_dims / 2;
     const float p = static_cast<float>(position);
+    const bool swizzled = s.dense_cache && mlr_cache_swizzled(sizeof(T) == 2, s.dim);
     if (qk_norm == 2) {
         // The root mean square of a whole projection: every thread sums its columns, the warps' sums are added in order.
         for (int which = 0; which < (k ? 2 : 1); ++which) {
@@ -195,11 +200,12 @@ __global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int l
         }
         for (int c = lane; c < n; c += 32) mine[c] = mine[c] * inv * (weight ? weight[c] : 1.0f);     // a lane's own values
         __syncwarp();
-        if (kind == 0) {
+        if (kind == 0 && !s.dense_cache) {
             T* dst = q + static_cast<size_t>(row) * ldq + static_cast<size_t>(head) * n;
             for (int c = lane; c < n; c += 32) mlr_store(dst, c, mine[c]);
-        } else if (kind == 1) {
-            T* dst = kbase + static_cast<size_t>(head) * page_size * s.dim;
+        } else if (kind < 2) {
+            // Keys go to the cache rotated; queries are rotated here only for kernels that do not rotate them as they load them.
+            T* dst = kind == 0 ? q + static_cast<size_t>(row) * ldq + static_cast<size_t>(head) * n : kbase + static_cast<size_t>(head) * page_size * s.dim;
             for (int c = lane; c < n; c += 32) {
                 float value = mine[c];
                 if (c < s.rot_dims) {
@@ -208,7 +214,7 @@ __global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int l
                     const float other = mine[c < half ? c + half : c - half];
                     value = c < half ? value * cs - other * sn : value * cs + other * sn;
                 }
-                mlr_store(dst, c, value);
+                mlr_store(dst, kind == 1 ? mlr_cache_col(c, position, swizzled) : c, value);
             }
         } else {
             T* dst = vbase + static_cast<size_t>(head) * page_size * s.vdim;
@@ -217,7 +223,7 @@ __global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int l
                 float value = mine[c];
                 if (mix == 1) keep[c] = value;
                 else if (mix == 2) value = (1.0f - lambda) * value + lambda * __ldcg(keep + c);
-                mlr_store(dst, c, value);
+                mlr_store(dst, mlr_cache_col(c, position, swizzled), value);
             }
         }
         __syncwarp();
@@ -1096,6 +1102,7 @@ int check_spec(const MaskedAttentionSpec* s, const char* who) {
     MLR_REQUIRE(!s->shared_kv || s->vdim <= s->dim, "%s: values that are the start of their keys cannot be longer, %d against %d", who, s->vdim, s->dim);
     MLR_REQUIRE(s->keep_first >= 0 && (s->keep_first == 0 || (s->window > 0 && s->chunk == 0)), "%s: kept first tokens go with a window and without chunks", who);
     MLR_REQUIRE(s->gate_kind >= 0 && s->gate_kind <= 3 && (!s->sinks || s->sink), "%s: bad gate kind, or sink scores without a sink", who);
+    MLR_REQUIRE(!s->dense_cache || (s->dim == s->vdim && !s->shared_kv), "%s: the plain attention kernels' cache has keys and values of one size", who);
     return 0;
 }
 

@@ -41,7 +41,7 @@ def sokolorn_plan(cfg: SokolornConfig) -> ModelPlan:
             params.update({"qk_norm": "whole", "window": m.window, "sink": "learned", "gate": "sigmoid_head"})
         else:
             names.update({f"{role}_bias": f"{p}mix.{role}.b" for role in (("q", "k", "v") if own_kv else ("q",))})
-            params.update({"qk_norm": "head", "bias": True})
+            params.update({"qk_norm": "head", "bias": True, "dense_kernels": True})
             if m.rot is not None:
                 s = m.rot.scaling
                 params["position"] = f"rot{i}"

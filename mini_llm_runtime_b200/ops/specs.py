@@ -19,6 +19,7 @@ class MaskedAttentionSpec(ctypes.Structure):
                 ("heads", ctypes.c_int32), ("kv_heads", ctypes.c_int32), ("dim", ctypes.c_int32), ("vdim", ctypes.c_int32),
                 ("rot_dims", ctypes.c_int32), ("window", ctypes.c_int32), ("chunk", ctypes.c_int32), ("sink", ctypes.c_int32),
                 ("gate_kind", ctypes.c_int32), ("shared_kv", ctypes.c_int32), ("keep_first", ctypes.c_int32), ("qk_norm", ctypes.c_int32),
+                ("dense_cache", ctypes.c_int32),
                 ("scale", ctypes.c_float), ("out_scale", ctypes.c_float), ("softcap", ctypes.c_float)]
 
 

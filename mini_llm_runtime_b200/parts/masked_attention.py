@@ -34,6 +34,10 @@ Further parameters, all off unless named (with any of the first four the step's 
                 its root mean square, times a weight of its size ("q_norm" [H D], "k_norm" [G D])
     own_kv      False: the layer reads the keys and values that the run named by its `Run.kv_from` cached (as that cache holds
                 them: normed, rotated) and has no "k", "v", "k_norm" and no biases but "q_bias"
+    dense_kernels   True: where the layer is plain causal (or windowed) attention after its preparation (keys and values of one size
+                up to 256; no chunk, sink, gate, cap, slopes, kept tokens, value mixing), `mlr_qkv_prepare_cache` also rotates the
+                queries and writes the cache as the kernels of the `attention` part read it, and those run: tcgen05 flash attention
+                for prompt portions, split-KV for decoded tokens (`ops/attention.py`).  Asked for where it does not fit, it is ignored.
 """
 from __future__ import annotations
 
@@ -43,6 +47,7 @@ import torch
 
 from ..config.base import ConfigError
 from ..config.registry import register_part
+from ..ops import attention as A
 from ..ops import functions as F
 from ..ops import native
 from ..ops.specs import GATES, QK_NORMS, MaskedAttentionSpec, address
@@ -87,6 +92,9 @@ class MaskedAttentionMixer(SequenceCore):
             raise ConfigError("dividing heads by their root mean square needs a positive eps")
         self.position_name = p.get("position")
         self.position = None
+        self.dense = (bool(p.get("dense_kernels")) and self.dim == self.vdim and self.dim <= 256 and self.chunk is None and not self.sink
+                      and self.gate is None and not self.softcap and self.slopes is None and not self.keep_first
+                      and self.value_mix is None and not self.unit_v)
         if self.heads % self.kv_heads:
             raise ConfigError(f"{self.heads} query heads cannot share {self.kv_heads} kv heads")
         if self.gate not in GATES:
@@ -107,6 +115,8 @@ class MaskedAttentionMixer(SequenceCore):
 
     def cache_need(self) -> CacheNeed:
         # Kept first tokens lie before the window: such a cache gives no pages back (the window is then a mask only).
+        if self.dense:
+            return CacheNeed(self.window, self.kv_heads, self.dim)      # the pool of the plain attention kernels
         return CacheNeed(None if self.keep_first else self.window, self.kv_heads, self.dim, self.vdim)
 
     def in_roles(self) -> List[Tuple[str, int]]:
@@ -138,13 +148,13 @@ class MaskedAttentionMixer(SequenceCore):
 
     @property
     def _prepares(self) -> bool:
-        return self.bias or self.unit_qk or self.unit_v or self.value_mix is not None or self.qk_norm is not None
+        return self.bias or self.unit_qk or self.unit_v or self.value_mix is not None or self.qk_norm is not None or self.dense
 
     def core_width(self) -> int:
         return self.heads * self.vdim
 
     def kernel_modules(self, dtype) -> List[str]:
-        return ["attention_masked"] + F.product_modules(dtype)
+        return ["attention_masked"] + (A.modules_for(dtype, self.dim) if self.dense else []) + F.product_modules(dtype)
 
     def bind_core(self, tensors, rt, out_scale: float) -> None:
         freq = self.position.frequencies() if self.position is not None else None
@@ -167,7 +177,9 @@ class MaskedAttentionMixer(SequenceCore):
             heads=self.heads, kv_heads=self.kv_heads, dim=self.dim,
             vdim=self.vdim, rot_dims=self.position.dims if self.position is not None else 0, window=self.window or 0,
             chunk=self.chunk or 0, sink=int(self.sink), gate_kind=GATES[self.gate], keep_first=self.keep_first, scale=self.scale,
-            out_scale=float(out_scale), softcap=self.softcap)
+            out_scale=float(out_scale), softcap=self.softcap, dense_cache=int(self.dense))
+        if self.dense and out_scale != 1.0:
+            raise ConfigError("the plain attention kernels scale no result; this mixer stands alone")
 
     def emit_core(self, b, proj, act, run: RunContext) -> None:
         if run.cache is None or run.cache.dtype is not proj.dtype:
@@ -199,6 +211,11 @@ class MaskedAttentionMixer(SequenceCore):
             b.launch("attention_masked", "mlr_kv_rope_cache", address(self.desc), k.ptr, k.ld, v.ptr, v.ld, proj.is_bf16,
                      run.cache.data_ptr(), run.cache.shape[0], b.meta("positions"), b.meta("segment_of_row"), table, stride,
                      b.page_size, proj.rows, b.status, b.stream)
+        if self.dense:
+            if act.ld != self.heads * self.vdim:
+                raise native.KernelError("masked attention: the plain attention kernels write a result of its own width")
+            A.paged_attention(b, proj, act, run.cache, run.group, self.heads, self.kv_heads, self.dim, self.window or 0, self.scale)
+            return
         emit_masked_attention(b, self.desc, proj, gate, act, run, self.FINER)
 
 

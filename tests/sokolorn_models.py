@@ -92,6 +92,21 @@ SMALL_C = {
     ],
 }
 
+# Rotated layers whose keys and values have one size, as the tcgen05 prompt kernel and the split-KV kernel take them (heads of 64 and
+# 128, the cache rows swizzled), beside one of 32; readers of each; a windowed layer of 64 that stays on the masked kernels.
+ROT_D = _rot(5000.0, 32, (4.0, 1.0, 4.0, 128))
+SMALL_D = {
+    "architecture": "Sokolorn", "vocab": 150, "width": 128, "norm": {"eps": 1e-6}, "logit_softcap": 20.0,
+    "layers": [
+        _rotary(4, 2, 64, 64, 0.12, _dense(96), rot=ROT_D),
+        _windowed(2, 2, 64, 64, 0.15, _moe(6, 2, 32, 1.2, shared=(40, 0.9)), window=40),
+        _rotary(2, 2, 64, 64, 0.1, _dense(64), rot=ROT_D, kv_from=0),
+        _rotary(2, 1, 128, 128, 0.09, None, rot=_rot(100.0, 128)),
+        _rotary(4, 1, 128, 128, 0.08, _dense(48), rot=_rot(100.0, 128), kv_from=3),
+        _rotary(4, 4, 32, 32, 0.2, _dense(48)),
+    ],
+}
+
 # One kind of mixer only, each in a model of its own.
 ONLY_WINDOWED = {
     "architecture": "Sokolorn", "vocab": 61, "width": 32, "norm": {"eps": 1e-5}, "logit_softcap": 5.0,
@@ -104,7 +119,7 @@ ONLY_ROTARY = {
                _rotary(4, 1, 16, 16, 0.2, _dense(16), rot=_rot(20.0, 4, (4.0, 1.0, 4.0, 16)), kv_from=0)],
 }
 
-ALL = {"small_a": SMALL_A, "small_b": SMALL_B, "small_c": SMALL_C, "only_windowed": ONLY_WINDOWED, "only_rotary": ONLY_ROTARY}
+ALL = {"small_a": SMALL_A, "small_b": SMALL_B, "small_c": SMALL_C, "small_d": SMALL_D, "only_windowed": ONLY_WINDOWED, "only_rotary": ONLY_ROTARY}
 
 
 def get(name: str) -> dict:

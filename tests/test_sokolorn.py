@@ -291,6 +291,52 @@ def _mixer_case(kind, dtype, heads, kv_heads, dim, vdim, T, page, how="rows", wi
     return out.double().cpu()[rows], want.reshape(T, heads * vdim)[rows], vd, shown
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,rot_dims", [(4, 2, 64, 32), (2, 1, 128, 128), (3, 3, 16, 8), (2, 2, 40, 0)])
+def test_preparation_for_the_plain_attention_kernels(dtype, heads, kv_heads, dim, rot_dims):
+    """With `dense_cache` the launch rotates the queries in place and writes keys and values as the kernels of plain causal
+    attention read them: [page][K | V][kv head][token][dim], the 16-byte chunks of a bfloat16 row of 64, 128 or 256 values
+    exchanged by the position's last three bits."""
+    from mini_llm_runtime_b200.ops import native
+    from mini_llm_runtime_b200.ops.specs import MaskedAttentionSpec
+    dev, T, page = "cuda:0", 37, 8
+    g = torch.Generator().manual_seed(dim)
+    q, k, v = (torch.randn(T, n, generator=g) for n in (heads * dim, kv_heads * dim, kv_heads * dim))
+    bq, bk, bv = (0.3 * torch.randn(n, generator=g) for n in (heads * dim, kv_heads * dim, kv_heads * dim))
+    wq, wk = 1.0 + 0.2 * torch.randn(dim, generator=g), 1.0 + 0.2 * torch.randn(dim, generator=g)
+    freqs = plain.scaled_frequencies(300.0, rot_dims, {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 32}) if rot_dims else []
+    freq_dev = torch.tensor(freqs, dtype=torch.float32, device=dev) if rot_dims else None
+    q, k, v = (x.to(dtype).to(dev) for x in (q, k, v))
+    keep = [t.float().to(dev) for t in (bq, bk, bv, wq, wk)]
+    spec = MaskedAttentionSpec(freq=freq_dev.data_ptr() if rot_dims else None, sinks=None, slopes=None, q_weight=keep[3].data_ptr(),
+                               k_weight=keep[4].data_ptr(), heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, rot_dims=rot_dims, window=0, chunk=0,
+                               sink=0, gate_kind=0, shared_kv=0, keep_first=0, qk_norm=1, dense_cache=1, scale=1.0, out_scale=1.0, softcap=0.0)
+    cache, n_pages, table = _pages(T, page, 2 * kv_heads * dim, dtype, g, dev)
+    positions, of_row, _ = _meta([(0, T, 0, 0)], dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    raw_q = q.clone()
+    _call("attention_masked", "mlr_qkv_prepare_cache", ctypes.addressof(spec), q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(),
+          v.stride(0), native.is_bf16(q), keep[0].data_ptr(), keep[1].data_ptr(), keep[2].data_ptr(), 0, 0, 1e-5, None, 0, 0, 0.0, cache.data_ptr(),
+          n_pages, positions.data_ptr(), of_row.data_ptr(), table.data_ptr(), table.stride(0), page, T, status.data_ptr(), native.stream())
+    assert int(status.item()) == 0
+    at = torch.arange(T)
+    want_q = plain.rotate_halves(plain.rms_norm((raw_q.double().cpu() + bq.double()).view(T, heads, dim), wq.double(), 1e-5), at, freqs)
+    want_k = plain.rotate_halves(plain.rms_norm((k.double().cpu() + bk.double()).view(T, kv_heads, dim), wk.double(), 1e-5), at, freqs)
+    want_v = (v.double().cpu() + bv.double()).view(T, kv_heads, dim)
+    tol = 2e-5 if dtype is torch.float32 else 2e-2
+    assert torch.allclose(q.double().cpu().view(T, heads, dim), want_q, atol=tol, rtol=tol)
+    held = cache.double().cpu().view(n_pages, 2, kv_heads, page, dim)
+    swizzled = dtype is torch.bfloat16 and dim in (64, 128, 256)
+    for t in range(T):
+        cols = torch.arange(dim)
+        if swizzled:
+            cols = cols ^ ((t & 7) << 3)
+        where = held[int(table[0, t // page])][:, :, t % page][:, :, cols]          # [K | V][kv head][dim], columns put back
+        assert torch.allclose(where[0], want_k[t], atol=tol, rtol=tol), t
+        assert torch.allclose(where[1], want_v[t], atol=tol, rtol=tol), t
+
+
 SCALED = {"base": 100.0, "dims": 8, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}}
 
 
