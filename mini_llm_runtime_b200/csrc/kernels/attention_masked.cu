@@ -62,6 +62,7 @@ namespace {
 
 constexpr int kTile = 64;
 constexpr int kThreads = 128;
+constexpr int kPrepareThreads = 1024; // the most threads of a block of `qkv_prepare_cache_kernel` (it is launched with 128 unless few rows need a whole norm)
 constexpr int kMaxDimsPerThread = 8;  // vdim <= 1024; the kernels are built for 2 (vdim <= 256), 4 and 8 value columns a thread
 constexpr int kRowsPerItem = 16;      // a segment that the planner gives the row kernel brings at most this many rows
 
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(kThreads) kv_rope_cache_kernel(const T* k, int
 // `first` is a float32 buffer of the step, [rows, kv_heads * vdim]: the values the first of several layers made of the same
 // tokens, which the later ones mix into their own.  All arithmetic is float32.
 template <typename T>
-__global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int ldq, const T* k, int ld_k, const T* v, int ld_v, const float* bq,
+__global__ void __launch_bounds__(kPrepareThreads) qkv_prepare_cache_kernel(T* q, int ldq, const T* k, int ld_k, const T* v, int ld_v, const float* bq,
                                                                      const float* bk, const float* bv, int unit_qk, int unit_v, float eps,
                                                                      float* first, int ld_first, int mix, float lambda, T* cache, int num_pages,
                                                                      const int* positions, const int* segment_of_row, const int* block_table,
@@ -132,7 +133,8 @@ __global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int l
     const int qk_norm = s.qk_norm;
     mlr_grid_wait();
     extern __shared__ __align__(16) float staged[];        // [warps][max(dim, vdim)]
-    __shared__ float whole_sum[kThreads / 32];
+    __shared__ float whole_sum[kPrepareThreads / 32];
+    const int threads = blockDim.x, warps = threads >> 5;        // 128, or up to 1024 (a warp a head) for few rows under a whole norm
     __shared__ float whole_inv[2];
     const int row = blockIdx.x;
     const int position = positions[row];
@@ -160,7 +162,7 @@ __global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int l
             const float* bias = which == 0 ? bq : bk;
             const int total = (which == 0 ? s.heads : s.kv_heads) * s.dim;
             float squares = 0.0f;
-            for (int c = threadIdx.x; c < total; c += kThreads) {
+            for (int c = threadIdx.x; c < total; c += threads) {
                 const float value = mlr_load(src, c) + (bias ? bias[c] : 0.0f);
                 squares = fmaf(value, value, squares);
             }
@@ -169,14 +171,14 @@ __global__ void __launch_bounds__(kThreads) qkv_prepare_cache_kernel(T* q, int l
             __syncthreads();
             if (threadIdx.x == 0) {
                 float sum = 0.0f;
-                for (int w = 0; w < kThreads / 32; ++w) sum += whole_sum[w];
+                for (int w = 0; w < warps; ++w) sum += whole_sum[w];
                 whole_inv[which] = 1.0f / sqrtf(sum / static_cast<float>(total) + eps);
             }
             __syncthreads();
         }
     }
     const int units = k ? s.heads + 2 * s.kv_heads : s.heads;
-    for (int unit = blockIdx.y * (kThreads / 32) + warp; unit < units; unit += gridDim.y * (kThreads / 32)) {
+    for (int unit = blockIdx.y * warps + warp; unit < units; unit += gridDim.y * warps) {
         const int kind = unit < s.heads ? 0 : (unit < s.heads + s.kv_heads ? 1 : 2);
         const int head = kind == 0 ? unit : (kind == 1 ? unit - s.heads : unit - s.heads - s.kv_heads);
         const int n = kind == 2 ? s.vdim : s.dim;
@@ -1148,20 +1150,29 @@ MLR_API int mlr_qkv_prepare_cache(const MaskedAttentionSpec* spec, void* q, int 
     MLR_REQUIRE(qk_norm >= 0 && qk_norm <= 2 && (qk_norm == 0 || (wq && (wk || !own_kv) && eps > 0.0f)),
                 "qkv_prepare_cache: a weighted norm of q and k needs its weights and a positive eps");
     if (rows == 0) return 0;
-    const size_t shared = sizeof(float) * (kThreads / 32) * static_cast<size_t>(spec->dim > spec->vdim ? spec->dim : spec->vdim);
+    // A norm over the whole projection reads all of q before any of it is changed: one block a row; with few rows that block gets a
+    // warp per head (up to 32), so that the heads' loads are in flight together.
+    const int all_units = own_kv ? spec->heads + 2 * spec->kv_heads : spec->heads;
+    int threads = kThreads;
+    if (qk_norm == 2 && rows <= 64) threads = 32 * (all_units < 32 ? (all_units < 4 ? 4 : all_units) : 32);
+    const size_t shared = sizeof(float) * (threads / 32) * static_cast<size_t>(spec->dim > spec->vdim ? spec->dim : spec->vdim);
+    MLR_REQUIRE(shared <= 160 * 1024, "qkv_prepare_cache: heads of %d values do not fit shared memory", spec->dim > spec->vdim ? spec->dim : spec->vdim);
     // With few rows (decoded tokens) every warp takes one head of q, k or v; with many, a block of four warps walks its row's
-    // heads in turn, which the same number of blocks in flight does a little faster.  A norm over the whole projection reads all
-    // of q before any of it is changed: one block a row.
-    const int units = own_kv ? spec->heads + 2 * spec->kv_heads : spec->heads, warps = kThreads / 32;
+    // heads in turn, which the same number of blocks in flight does a little faster.
+    const int units = all_units, warps = threads / 32;
     const int wanted = rows >= 592 || qk_norm == 2 ? 1 : (592 + rows - 1) / rows, most = (units + warps - 1) / warps;
     const dim3 grid(rows, wanted < most ? wanted : most);
+    if (shared > 48 * 1024) {
+        cudaFuncSetAttribute(qkv_prepare_cache_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+        cudaFuncSetAttribute(qkv_prepare_cache_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+    }
     if (act_bf16)
-        mlr_launch((qkv_prepare_cache_kernel<__nv_bfloat16>), dim3(grid), dim3(kThreads), shared, stream, static_cast<__nv_bfloat16*>(q), ldq,
+        mlr_launch((qkv_prepare_cache_kernel<__nv_bfloat16>), dim3(grid), dim3(threads), shared, stream, static_cast<__nv_bfloat16*>(q), ldq,
                    static_cast<const __nv_bfloat16*>(k), ld_k, static_cast<const __nv_bfloat16*>(v), ld_v, bq, bk, bv, unit_qk, unit_v, eps, first,
                    ld_first, mix, lambda, static_cast<__nv_bfloat16*>(cache), num_pages, positions, segment_of_row, block_table, table_stride,
                    page_size, *spec, status);
     else
-        mlr_launch((qkv_prepare_cache_kernel<float>), dim3(grid), dim3(kThreads), shared, stream, static_cast<float*>(q), ldq,
+        mlr_launch((qkv_prepare_cache_kernel<float>), dim3(grid), dim3(threads), shared, stream, static_cast<float*>(q), ldq,
                    static_cast<const float*>(k), ld_k, static_cast<const float*>(v), ld_v, bq, bk, bv, unit_qk, unit_v, eps, first, ld_first, mix,
                    lambda, static_cast<float*>(cache), num_pages, positions, segment_of_row, block_table, table_stride, page_size, *spec, status);
     return mlr_launched("qkv_prepare_cache");

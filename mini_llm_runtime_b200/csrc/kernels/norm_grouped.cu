@@ -45,7 +45,15 @@ __device__ __forceinline__ void group_inverse_rms(const float* vals, float* inv,
     }
 }
 
-template <typename T>
+__device__ __forceinline__ void store4(float* o, int i, float4 v) { *reinterpret_cast<float4*>(o + i) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* o, int i, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(o + i) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
+// VEC: four values an access (the width and every row stride are multiples of 4 and the rows start on 16-byte borders); the
+// arithmetic and the order of every sum are the same as one value at a time.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(kThreads) group_rmsnorm_kernel(float* h, const float* delta, int ld_delta, const float* bias,
                                                                  const float* w_post, const float* w_pre, T* out, int ld_out,
                                                                  const int* rows, int width, int groups, float eps, int mode) {
@@ -57,34 +65,74 @@ __global__ void __launch_bounds__(kThreads) group_rmsnorm_kernel(float* h, const
     const int row = rows ? rows[blockIdx.x] : blockIdx.x;
     const int part = width / groups;
     float* hrow = h + static_cast<size_t>(row) * width;
+    constexpr int kStep = VEC ? 4 : 1;
+    auto load = [](const float* p, int i) {
+        if constexpr (VEC) return __ldcg(reinterpret_cast<const float4*>(p + i));
+        else return make_float4(p[i], 0.0f, 0.0f, 0.0f);
+    };
+    auto keep = [&](int i, float4 v) {
+        if constexpr (VEC) *reinterpret_cast<float4*>(vals + i) = v;
+        else vals[i] = v.x;
+    };
+    auto kept = [&](int i) {
+        if constexpr (VEC) return *reinterpret_cast<const float4*>(vals + i);
+        else return make_float4(vals[i], 0.0f, 0.0f, 0.0f);
+    };
     if (delta) {
         const float* d = delta + static_cast<size_t>(row) * ld_delta;
-        for (int i = threadIdx.x; i < width; i += kThreads) vals[i] = d[i] + (bias ? bias[i] : 0.0f);
+        for (int i = threadIdx.x * kStep; i < width; i += kThreads * kStep) {
+            float4 v = load(d, i);
+            if (bias) {
+                const float4 b = load(bias, i);
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+            }
+            keep(i, v);
+        }
         __syncthreads();
         if (norm_delta) group_inverse_rms(vals, inv, width, groups, eps);
         __syncthreads();
-        for (int i = threadIdx.x; i < width; i += kThreads) {
-            const float normed = norm_delta ? vals[i] * inv[i / part] : vals[i];
-            const float sum = hrow[i] + (w_post ? normed * w_post[i] : normed);
-            hrow[i] = sum;
-            vals[i] = sum;
+        for (int i = threadIdx.x * kStep; i < width; i += kThreads * kStep) {
+            float4 v = kept(i);
+            if (norm_delta) {
+                v.x *= inv[i / part];
+                if constexpr (VEC) { v.y *= inv[(i + 1) / part]; v.z *= inv[(i + 2) / part]; v.w *= inv[(i + 3) / part]; }
+            }
+            if (w_post) {
+                const float4 w = load(w_post, i);
+                v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
+            }
+            const float4 old = load(hrow, i);
+            v.x = old.x + v.x; v.y = old.y + v.y; v.z = old.z + v.z; v.w = old.w + v.w;
+            if constexpr (VEC) *reinterpret_cast<float4*>(hrow + i) = v;
+            else hrow[i] = v.x;
+            keep(i, v);
         }
     } else {
-        for (int i = threadIdx.x; i < width; i += kThreads) vals[i] = hrow[i];
+        for (int i = threadIdx.x * kStep; i < width; i += kThreads * kStep) keep(i, load(hrow, i));
     }
     if (!out) return;
     T* o = out + static_cast<size_t>(blockIdx.x) * ld_out;
     if (plain_out) {           // every thread wrote the values it reads back
-        for (int i = threadIdx.x; i < width; i += kThreads) mlr_store(o, i, vals[i]);
+        for (int i = threadIdx.x * kStep; i < width; i += kThreads * kStep) {
+            if constexpr (VEC) store4(o, i, kept(i));
+            else mlr_store(o, i, vals[i]);
+        }
         mlr_grid_dependents_may_start();
         return;
     }
     __syncthreads();
     group_inverse_rms(vals, inv, width, groups, eps);
     __syncthreads();
-    for (int i = threadIdx.x; i < width; i += kThreads) {
-        const float normed = vals[i] * inv[i / part];
-        mlr_store(o, i, w_pre ? normed * w_pre[i] : normed);
+    for (int i = threadIdx.x * kStep; i < width; i += kThreads * kStep) {
+        float4 v = kept(i);
+        v.x *= inv[i / part];
+        if constexpr (VEC) { v.y *= inv[(i + 1) / part]; v.z *= inv[(i + 2) / part]; v.w *= inv[(i + 3) / part]; }
+        if (w_pre) {
+            const float4 w = load(w_pre, i);
+            v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
+        }
+        if constexpr (VEC) store4(o, i, v);
+        else mlr_store(o, i, v.x);
     }
     mlr_grid_dependents_may_start();
 }
@@ -103,15 +151,23 @@ MLR_API int mlr_group_rmsnorm(float* h, const float* delta, int ld_delta, const 
     if (count == 0) return 0;
     const size_t shared = sizeof(float) * (static_cast<size_t>(width) + groups + kThreads / 32);
     MLR_REQUIRE(shared <= 200 * 1024, "group_rmsnorm: a row of %d values does not fit shared memory", width);
-    if (shared > 48 * 1024) {
-        cudaFuncSetAttribute(group_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-        cudaFuncSetAttribute(group_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+    const auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const bool vec = width % 4 == 0 && ld_delta % 4 == 0 && ld_out % 4 == 0 && aligned(h) && aligned(delta) && aligned(bias) && aligned(w_post) &&
+                     aligned(w_pre) && aligned(out);
+#define MLR_NORM(T, VEC)                                                                                                               \
+    do {                                                                                                                               \
+        if (shared > 48 * 1024)                                                                                                        \
+            cudaFuncSetAttribute(group_rmsnorm_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)); \
+        mlr_launch((group_rmsnorm_kernel<T, VEC>), dim3(count), dim3(kThreads), shared, stream, h, delta, ld_delta, bias, w_post, w_pre, \
+                   static_cast<T*>(out), ld_out, rows, width, groups, eps, norm_delta);                                               \
+    } while (0)
+    if (out_bf16) {
+        if (vec) MLR_NORM(__nv_bfloat16, true);
+        else MLR_NORM(__nv_bfloat16, false);
+    } else {
+        if (vec) MLR_NORM(float, true);
+        else MLR_NORM(float, false);
     }
-    if (out_bf16)
-        mlr_launch((group_rmsnorm_kernel<__nv_bfloat16>), dim3(count), dim3(kThreads), shared, stream, h, delta, ld_delta, bias, w_post,
-                   w_pre, static_cast<__nv_bfloat16*>(out), ld_out, rows, width, groups, eps, norm_delta);
-    else
-        mlr_launch((group_rmsnorm_kernel<float>), dim3(count), dim3(kThreads), shared, stream, h, delta, ld_delta, bias, w_post, w_pre,
-                   static_cast<float*>(out), ld_out, rows, width, groups, eps, norm_delta);
+#undef MLR_NORM
     return mlr_launched("group_rmsnorm");
 }
