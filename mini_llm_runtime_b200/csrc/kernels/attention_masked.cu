@@ -122,8 +122,8 @@ __global__ void __launch_bounds__(kThreads) kv_rope_cache_kernel(const T* k, int
 // Without k (a layer that reads the keys and values another layer cached) only the queries are prepared.
 // `first` is a float32 buffer of the step, [rows, kv_heads * vdim]: the values the first of several layers made of the same
 // tokens, which the later ones mix into their own.  All arithmetic is float32.
-template <typename T>
-__global__ void __launch_bounds__(kPrepareThreads) qkv_prepare_cache_kernel(T* q, int ldq, const T* k, int ld_k, const T* v, int ld_v, const float* bq,
+template <typename T, int kBlock>
+__global__ void __launch_bounds__(kBlock) qkv_prepare_cache_kernel(T* q, int ldq, const T* k, int ld_k, const T* v, int ld_v, const float* bq,
                                                                      const float* bk, const float* bv, int unit_qk, int unit_v, float eps,
                                                                      float* first, int ld_first, int mix, float lambda, T* cache, int num_pages,
                                                                      const int* positions, const int* segment_of_row, const int* block_table,
@@ -133,8 +133,9 @@ __global__ void __launch_bounds__(kPrepareThreads) qkv_prepare_cache_kernel(T* q
     const int qk_norm = s.qk_norm;
     mlr_grid_wait();
     extern __shared__ __align__(16) float staged[];        // [warps][max(dim, vdim)]
-    __shared__ float whole_sum[kPrepareThreads / 32];
-    const int threads = blockDim.x, warps = threads >> 5;        // 128, or up to 1024 (a warp a head) for few rows under a whole norm
+    __shared__ float whole_sum[kBlock / 32];
+    // kBlock: 128, or 1024 (a warp a head, launched with as many warps as there are heads) for few rows under a whole norm
+    const int threads = kBlock == kThreads ? kThreads : static_cast<int>(blockDim.x), warps = threads >> 5;
     __shared__ float whole_inv[2];
     const int row = blockIdx.x;
     const int position = positions[row];
@@ -1162,19 +1163,23 @@ MLR_API int mlr_qkv_prepare_cache(const MaskedAttentionSpec* spec, void* q, int 
     const int units = all_units, warps = threads / 32;
     const int wanted = rows >= 592 || qk_norm == 2 ? 1 : (592 + rows - 1) / rows, most = (units + warps - 1) / warps;
     const dim3 grid(rows, wanted < most ? wanted : most);
-    if (shared > 48 * 1024) {
-        cudaFuncSetAttribute(qkv_prepare_cache_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-        cudaFuncSetAttribute(qkv_prepare_cache_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+#define MLR_PREPARE(T, BLOCK)                                                                                                              \
+    do {                                                                                                                                   \
+        if (shared > 48 * 1024)                                                                                                            \
+            cudaFuncSetAttribute(qkv_prepare_cache_kernel<T, BLOCK>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)); \
+        mlr_launch((qkv_prepare_cache_kernel<T, BLOCK>), dim3(grid), dim3(threads), shared, stream, static_cast<T*>(q), ldq,               \
+                   static_cast<const T*>(k), ld_k, static_cast<const T*>(v), ld_v, bq, bk, bv, unit_qk, unit_v, eps, first, ld_first, mix, \
+                   lambda, static_cast<T*>(cache), num_pages, positions, segment_of_row, block_table, table_stride, page_size, *spec,      \
+                   status);                                                                                                                \
+    } while (0)
+    if (act_bf16) {
+        if (threads == kThreads) MLR_PREPARE(__nv_bfloat16, kThreads);
+        else MLR_PREPARE(__nv_bfloat16, kPrepareThreads);
+    } else {
+        if (threads == kThreads) MLR_PREPARE(float, kThreads);
+        else MLR_PREPARE(float, kPrepareThreads);
     }
-    if (act_bf16)
-        mlr_launch((qkv_prepare_cache_kernel<__nv_bfloat16>), dim3(grid), dim3(threads), shared, stream, static_cast<__nv_bfloat16*>(q), ldq,
-                   static_cast<const __nv_bfloat16*>(k), ld_k, static_cast<const __nv_bfloat16*>(v), ld_v, bq, bk, bv, unit_qk, unit_v, eps, first,
-                   ld_first, mix, lambda, static_cast<__nv_bfloat16*>(cache), num_pages, positions, segment_of_row, block_table, table_stride,
-                   page_size, *spec, status);
-    else
-        mlr_launch((qkv_prepare_cache_kernel<float>), dim3(grid), dim3(threads), shared, stream, static_cast<float*>(q), ldq,
-                   static_cast<const float*>(k), ld_k, static_cast<const float*>(v), ld_v, bq, bk, bv, unit_qk, unit_v, eps, first, ld_first, mix,
-                   lambda, static_cast<float*>(cache), num_pages, positions, segment_of_row, block_table, table_stride, page_size, *spec, status);
+#undef MLR_PREPARE
     return mlr_launched("qkv_prepare_cache");
 }
 

@@ -51,13 +51,30 @@ __device__ __forceinline__ void store4(__nv_bfloat16* o, int i, float4 v) {
     *reinterpret_cast<uint2*>(o + i) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
 }
 
+// A contribution that has not been added up yet: row t is  sum_j weights[t, j] * y[row_of_pair[t, j]]  (j = 0 .. top-1 in order)
+// + gate[t] * shared[t]  (the results of a token's routed experts, in rows ordered by expert, and of a shared expert).  y null:
+// the contribution is `delta` as it stands.
+struct Pieces {
+    const float* y;
+    long long ldy;
+    const int* row_of_pair;
+    const float* weights;
+    int top;
+    const float* shared;
+    long long ld_shared;
+    const float* gate;
+};
+constexpr int kMaxPieces = 32;
+
 // VEC: four values an access (the width and every row stride are multiples of 4 and the rows start on 16-byte borders); the
 // arithmetic and the order of every sum are the same as one value at a time.
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(kThreads) group_rmsnorm_kernel(float* h, const float* delta, int ld_delta, const float* bias,
                                                                  const float* w_post, const float* w_pre, T* out, int ld_out,
-                                                                 const int* rows, int width, int groups, float eps, int mode) {
+                                                                 const int* rows, int width, int groups, float eps, int mode, Pieces pieces) {
     const int norm_delta = mode & 1, plain_out = mode & 2;
+    __shared__ float piece_weight[kMaxPieces];
+    __shared__ long long piece_from[kMaxPieces];
     mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     float* vals = reinterpret_cast<float*>(smem);
@@ -78,10 +95,33 @@ __global__ void __launch_bounds__(kThreads) group_rmsnorm_kernel(float* h, const
         if constexpr (VEC) return *reinterpret_cast<const float4*>(vals + i);
         else return make_float4(vals[i], 0.0f, 0.0f, 0.0f);
     };
-    if (delta) {
+    if (delta || pieces.y) {
         const float* d = delta + static_cast<size_t>(row) * ld_delta;
+        if (pieces.y) {
+            if (threadIdx.x < pieces.top) {
+                piece_weight[threadIdx.x] = __ldcg(pieces.weights + static_cast<size_t>(row) * pieces.top + threadIdx.x);
+                piece_from[threadIdx.x] = static_cast<long long>(__ldcg(pieces.row_of_pair + static_cast<size_t>(row) * pieces.top + threadIdx.x)) * pieces.ldy;
+            }
+            __syncthreads();
+        }
+        const float shared_gate = pieces.y && pieces.shared && pieces.gate ? __ldcg(pieces.gate + row) : 1.0f;
         for (int i = threadIdx.x * kStep; i < width; i += kThreads * kStep) {
-            float4 v = load(d, i);
+            float4 v;
+            if (pieces.y) {
+                v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int j = 0; j < pieces.top; ++j) {
+                    const float4 e = load(pieces.y + piece_from[j], i);
+                    const float w = piece_weight[j];
+                    v.x = fmaf(w, e.x, v.x); v.y = fmaf(w, e.y, v.y); v.z = fmaf(w, e.z, v.z); v.w = fmaf(w, e.w, v.w);
+                }
+                if (pieces.shared) {
+                    const float4 e = load(pieces.shared + static_cast<size_t>(row) * pieces.ld_shared, i);
+                    if (pieces.gate) { v.x = fmaf(shared_gate, e.x, v.x); v.y = fmaf(shared_gate, e.y, v.y); v.z = fmaf(shared_gate, e.z, v.z); v.w = fmaf(shared_gate, e.w, v.w); }
+                    else { v.x += e.x; v.y += e.y; v.z += e.z; v.w += e.w; }
+                }
+            } else {
+                v = load(d, i);
+            }
             if (bias) {
                 const float4 b = load(bias, i);
                 v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
@@ -139,27 +179,31 @@ __global__ void __launch_bounds__(kThreads) group_rmsnorm_kernel(float* h, const
 
 }  // namespace
 
-MLR_API int mlr_group_rmsnorm(float* h, const float* delta, int ld_delta, const float* bias, const float* w_post,
-                              const float* w_pre, void* out, int ld_out, int out_bf16, const int* rows, int count, int width,
-                              int groups, float eps, int norm_delta, cudaStream_t stream) {
+namespace {
+int group_rmsnorm(float* h, const float* delta, int ld_delta, const float* bias, const float* w_post, const float* w_pre, void* out, int ld_out,
+                  int out_bf16, const int* rows, int count, int width, int groups, float eps, int norm_delta, const Pieces& pieces,
+                  cudaStream_t stream) {
     MLR_REQUIRE(count >= 0 && width > 0 && groups > 0 && width % groups == 0,
                 "group_rmsnorm: width %d cannot be cut into %d equal groups", width, groups);
     MLR_REQUIRE(eps >= 0.0f, "group_rmsnorm: eps must not be negative");
-    MLR_REQUIRE(h && (delta || out), "group_rmsnorm: nothing to do");
+    MLR_REQUIRE(h && (delta || out || pieces.y), "group_rmsnorm: nothing to do");
     MLR_REQUIRE(!delta || (ld_delta >= width && !rows), "group_rmsnorm: a contribution is added for all rows, with a row stride >= width");
+    MLR_REQUIRE(!pieces.y || (!delta && !rows && pieces.top >= 1 && pieces.top <= kMaxPieces && pieces.row_of_pair && pieces.weights &&
+                              pieces.ldy >= width && (!pieces.shared || pieces.ld_shared >= width)),
+                "group_rmsnorm: a contribution in pieces stands instead of a plain one, for all rows, with at most %d pieces a row", kMaxPieces);
     MLR_REQUIRE(!out || ld_out >= width, "group_rmsnorm: the output's row stride is smaller than the width");
     if (count == 0) return 0;
     const size_t shared = sizeof(float) * (static_cast<size_t>(width) + groups + kThreads / 32);
     MLR_REQUIRE(shared <= 200 * 1024, "group_rmsnorm: a row of %d values does not fit shared memory", width);
     const auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
     const bool vec = width % 4 == 0 && ld_delta % 4 == 0 && ld_out % 4 == 0 && aligned(h) && aligned(delta) && aligned(bias) && aligned(w_post) &&
-                     aligned(w_pre) && aligned(out);
+                     aligned(w_pre) && aligned(out) && aligned(pieces.y) && pieces.ldy % 4 == 0 && aligned(pieces.shared) && pieces.ld_shared % 4 == 0;
 #define MLR_NORM(T, VEC)                                                                                                               \
     do {                                                                                                                               \
         if (shared > 48 * 1024)                                                                                                        \
             cudaFuncSetAttribute(group_rmsnorm_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)); \
         mlr_launch((group_rmsnorm_kernel<T, VEC>), dim3(count), dim3(kThreads), shared, stream, h, delta, ld_delta, bias, w_post, w_pre, \
-                   static_cast<T*>(out), ld_out, rows, width, groups, eps, norm_delta);                                               \
+                   static_cast<T*>(out), ld_out, rows, width, groups, eps, norm_delta, pieces);                                       \
     } while (0)
     if (out_bf16) {
         if (vec) MLR_NORM(__nv_bfloat16, true);
@@ -170,4 +214,24 @@ MLR_API int mlr_group_rmsnorm(float* h, const float* delta, int ld_delta, const 
     }
 #undef MLR_NORM
     return mlr_launched("group_rmsnorm");
+}
+}  // namespace
+
+MLR_API int mlr_group_rmsnorm(float* h, const float* delta, int ld_delta, const float* bias, const float* w_post,
+                              const float* w_pre, void* out, int ld_out, int out_bf16, const int* rows, int count, int width,
+                              int groups, float eps, int norm_delta, cudaStream_t stream) {
+    return group_rmsnorm(h, delta, ld_delta, bias, w_post, w_pre, out, ld_out, out_bf16, rows, count, width, groups, eps, norm_delta, Pieces{},
+                         stream);
+}
+
+// The same with the contribution given in pieces (see `Pieces`): what routed experts leave, added up here instead of by a launch
+// of its own.  y: float32 rows ordered by expert; row_of_pair, weights: [count, top]; shared: float32 [count, width] or null; gate:
+// float32 [count] or null (the shared expert's result then joins as it is).
+MLR_API int mlr_group_rmsnorm_pieces(float* h, const float* y, long long ldy, const int* row_of_pair, const float* weights, int top,
+                                     const float* shared_y, long long ld_shared, const float* gate, const float* w_post, const float* w_pre,
+                                     void* out, int ld_out, int out_bf16, int count, int width, int groups, float eps, int mode,
+                                     cudaStream_t stream) {
+    MLR_REQUIRE(y, "group_rmsnorm_pieces: no pieces");
+    const Pieces pieces = {y, ldy, row_of_pair, weights, top, shared_y, ld_shared, gate};
+    return group_rmsnorm(h, nullptr, 0, nullptr, w_post, w_pre, out, ld_out, out_bf16, nullptr, count, width, groups, eps, mode, pieces, stream);
 }

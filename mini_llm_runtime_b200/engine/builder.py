@@ -80,6 +80,10 @@ class Buf:
     # A float32 vector [width] that whoever adds this contribution into the stream must add to every row first
     # (the bias of a sub-layer's last product, which has no bias operand).
     bias: Optional[torch.Tensor] = None
+    # A contribution that has not been added up: `ptr` is None and this holds (y, row_of_pair, weights, top, shared or None,
+    # gate or None), the results of a token's routed experts (`parts/experts.py`).  Only a reader that said it takes them
+    # (`accepts_pieces` of the builder) is handed one.
+    pieces: Optional[tuple] = None
 
     @property
     def is_bf16(self) -> int:

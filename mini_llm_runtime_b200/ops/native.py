@@ -90,6 +90,8 @@ _SIGNATURES = {
     "norm_grouped": {
         "mlr_group_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                               c_int, c_float, c_int, c_void_p],
+        "mlr_group_rmsnorm_pieces": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     },
     "layernorm": {
         "mlr_depth_norm": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,

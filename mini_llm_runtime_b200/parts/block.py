@@ -81,7 +81,12 @@ class SandwichBlock(Block):
             ahead = self.norms["post_mixer"].emit_residual(b, h, mixed, then=following)
         else:
             x = self.norms["post_mixer"].emit_residual(b, h, mixed, then=self.norms["pre_feed_forward"])
-            out = self.feed_forward.emit(b, x)
+            # A feed-forward of routed experts may leave its result in pieces for the norm behind it to add up.
+            b.accepts_pieces = bool(getattr(self.norms["post_feed_forward"], "takes_pieces", False))
+            try:
+                out = self.feed_forward.emit(b, x)
+            finally:
+                b.accepts_pieces = False
             ahead = self.norms["post_feed_forward"].emit_residual(b, h, out, then=following)
         b.prepared = {"group_rms": following, "stream": h, "out": ahead} if following is not None else None
         return None

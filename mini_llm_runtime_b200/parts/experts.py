@@ -8,7 +8,8 @@ beside an optional shared one that every token uses.
 
 Launches: route (also counts every expert's tokens) -> arrange (rows in the order by expert, the products' row tiles)
 -> the gate/up product with the gate in its epilogue, over rows gathered from the tokens -> the down product
--> combine (weights, the shared expert and its gate).  The shared expert is the package's dense gated feed-forward.
+-> combine (weights, the shared expert and its gate; a block whose norm stands behind the sub-layer takes the pieces and
+combines them in that norm's launch: `Buf.pieces`).  The shared expert is the package's dense gated feed-forward.
 The products over the experts' rows read their row ranges from the device, so a step needs no answer from the GPU.
 
 Two choices differ between designs and are parameters.  `router`: "sigmoid_groups" is the rule above; "softmax_of_chosen"
@@ -133,6 +134,10 @@ class RoutedExperts(FeedForward):
         elif self.shared_inter:
             hidden = rt.gated_linear(b, x, self.shared_gate_up)
             shared = rt.linear(b, hidden, self.shared_down, out_dtype=f32)
+        if getattr(b, "accepts_pieces", False):
+            # Whoever adds this result into the stream adds the pieces up itself (the norm behind the sub-layer): no launch here.
+            from ..engine.builder import Buf
+            return Buf(None, rows, self.width, f32, self.width, pieces=(y, row_of_pair, weights, top, shared, gate))
         out = b.temp(rows, self.width, f32)
         b.launch("experts", "mlr_experts_combine", y.ptr, self.width, row_of_pair.ptr, weights.ptr, top, shared.ptr if shared else None,
                  shared.ld if shared else 0, 0, gate.ptr if gate else None, out.ptr, out.ld, rows, self.width, b.stream)

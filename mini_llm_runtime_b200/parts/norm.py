@@ -122,6 +122,8 @@ class GroupRmsNorm(Norm):
             return other.width == self.width
         return isinstance(other, GroupRmsNorm) and (other.width, other.groups, other.eps) == (self.width, self.groups, self.eps)
 
+    takes_pieces = True      # `emit_residual` adds up a contribution that routed experts left in pieces (`Buf.pieces`)
+
     def emit_residual(self, b, h, delta, then: Optional[Norm] = None):
         """h += norm(delta + its bias) * weight; returns then(h) in the activation dtype, or None."""
         if delta.slices:
@@ -134,10 +136,19 @@ class GroupRmsNorm(Norm):
         else:
             out = b.temp(h.rows, self.width, b.rt.dtype) if then is not None else None
         bias = getattr(delta, "bias", None)
-        b.launch("norm_grouped", "mlr_group_rmsnorm", h.ptr, delta.ptr, delta.ld, bias.data_ptr() if bias is not None else None,
-                 self.weight.data_ptr(), then.weight.data_ptr() if out is not None and not plain else None,
-                 out.ptr if out is not None else None, out.ld if out is not None else 0, int(b.rt.is_bf16), None, h.rows,
-                 self.width, self.groups, self.eps, 1 | (2 if plain else 0), b.stream)
+        w_pre = then.weight.data_ptr() if out is not None and not plain else None
+        if delta.pieces is not None:
+            y, row_of_pair, weights, top, shared, gate = delta.pieces
+            if bias is not None or y.dtype is not torch.float32 or (shared is not None and shared.dtype is not torch.float32):
+                raise native.KernelError("the grouped norm adds up float32 pieces without a bias")
+            b.launch("norm_grouped", "mlr_group_rmsnorm_pieces", h.ptr, y.ptr, self.width, row_of_pair.ptr, weights.ptr, top,
+                     shared.ptr if shared is not None else None, shared.ld if shared is not None else 0, gate.ptr if gate is not None else None,
+                     self.weight.data_ptr(), w_pre, out.ptr if out is not None else None, out.ld if out is not None else 0,
+                     int(b.rt.is_bf16), h.rows, self.width, self.groups, self.eps, 1 | (2 if plain else 0), b.stream)
+        else:
+            b.launch("norm_grouped", "mlr_group_rmsnorm", h.ptr, delta.ptr, delta.ld, bias.data_ptr() if bias is not None else None,
+                     self.weight.data_ptr(), w_pre, out.ptr if out is not None else None, out.ld if out is not None else 0,
+                     int(b.rt.is_bf16), None, h.rows, self.width, self.groups, self.eps, 1 | (2 if plain else 0), b.stream)
         if plain and then is None:
             return h
         if then is not None and out is None:

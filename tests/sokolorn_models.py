@@ -93,7 +93,7 @@ SMALL_C = {
 }
 
 # Rotated layers whose keys and values have one size, as the tcgen05 prompt kernel and the split-KV kernel take them (heads of 64 and
-# 128, the cache rows swizzled), beside one of 32; readers of each; a windowed layer of 64 that stays on the masked kernels.
+# 128, the cache rows swizzled), beside one of 32 and one of 24 (no tensor-core size); readers of each; a windowed layer of 64 that stays on the masked kernels.
 ROT_D = _rot(5000.0, 32, (4.0, 1.0, 4.0, 128))
 SMALL_D = {
     "architecture": "Sokolorn", "vocab": 150, "width": 128, "norm": {"eps": 1e-6}, "logit_softcap": 20.0,
@@ -104,6 +104,7 @@ SMALL_D = {
         _rotary(2, 1, 128, 128, 0.09, None, rot=_rot(100.0, 128)),
         _rotary(4, 1, 128, 128, 0.08, _dense(48), rot=_rot(100.0, 128), kv_from=3),
         _rotary(4, 4, 32, 32, 0.2, _dense(48)),
+        _rotary(6, 2, 24, 24, 0.2, None, rot=_rot(40.0, 12)),
     ],
 }
 
