@@ -171,6 +171,34 @@ def test_norm_behind_a_sub_layer_with_a_weight_stored_around_zero(dtype, width, 
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("rows,width,top,shared,gated", [(5, 48, 3, True, True), (70, 36, 1, False, False), (9, 256, 4, True, False), (300, 40, 2, True, True)])
+def test_norm_behind_routed_experts_adds_up_their_pieces(rows, width, top, shared, gated):
+    """The contribution given in pieces (a token's experts' results in rows ordered by expert, their weights, the shared expert's
+    result and its gate): the launch adds them up, norms the sum and adds it into the stream."""
+    from mini_llm_runtime_b200.ops import native
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(rows + width)
+    h = torch.randn(rows, width, generator=g)
+    y = torch.randn(rows * top, width, generator=g)
+    row_of_pair = torch.randperm(rows * top, generator=g).to(torch.int32).view(rows, top)
+    weights = torch.rand(rows, top, generator=g)
+    other = torch.randn(rows, width, generator=g)
+    gate = torch.rand(rows, generator=g)
+    w = 0.2 * torch.randn(width, generator=g)
+    hd, yd, rd, wd, od, gd, weight = (t.to(dev) for t in (h, y, row_of_pair, weights, other, gate, w + 1.0))
+    out = torch.full((rows, width), float("nan"), dtype=torch.bfloat16, device=dev)
+    _call("norm_grouped", "mlr_group_rmsnorm_pieces", hd.data_ptr(), yd.data_ptr(), width, rd.data_ptr(), wd.data_ptr(), top,
+          od.data_ptr() if shared else None, od.stride(0) if shared else 0, gd.data_ptr() if shared and gated else None, weight.data_ptr(), None,
+          out.data_ptr(), out.stride(0), 1, rows, width, 1, 1e-6, 3, native.stream())
+    total = (weights.double()[:, :, None] * y.double()[row_of_pair.long()]).sum(dim=1)
+    if shared:
+        total = total + (gate.double()[:, None] if gated else 1.0) * other.double()
+    want = h.double() + plain.rms_norm(total, w.double(), 1e-6, one_plus=True)
+    assert torch.allclose(hd.double().cpu(), want, atol=2e-5, rtol=2e-5), float((hd.double().cpu() - want).abs().max())
+    assert torch.equal(out.cpu(), hd.bfloat16().cpu())
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rows,width", [(3, 37), (70, 40), (2, 1024)])
 def test_squared_relu_and_the_cap_on_the_logits(dtype, rows, width):
