@@ -347,7 +347,7 @@ def sokolorn_config(width, ff, heads, kv, dim, layers, chunk, vocab):
     of the layer before it, dense; the first kind again with experts.  Logits from the embedding table, capped."""
     windowed = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": max(chunk // 2, 1)}}
     rotary = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-              "rot": {"base": 5e5, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}}}
+              "rot": {"base": 5e5, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     dense = {"kind": "dense", "ff": ff * 3 // 2}
     moe = {"kind": "moe", "expert": {"ff": ff // 6, "limit": 7.0}, "shared": {"ff": ff // 3, "limit": 7.0}, "router": {"experts": 16, "top": 4}}
     made = []

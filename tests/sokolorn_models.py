@@ -94,7 +94,7 @@ SMALL_C = {
 
 # Rotated layers whose keys and values have one size, as the tcgen05 prompt kernel and the split-KV kernel take them (heads of 64 and
 # 128, the cache rows swizzled), beside one of 32 and one of 24 (no tensor-core size); readers of each; a windowed layer of 64 that stays on the masked kernels.
-ROT_D = _rot(5000.0, 32, (4.0, 1.0, 4.0, 128))
+ROT_D = _rot(5000.0, 48, (2.0, 0.5, 3.0, 96))
 SMALL_D = {
     "architecture": "Sokolorn", "vocab": 150, "width": 128, "norm": {"eps": 1e-6}, "logit_softcap": 20.0,
     "layers": [

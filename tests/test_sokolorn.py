@@ -404,7 +404,7 @@ def test_the_same_in_tiles_on_the_tensor_cores(case):
 # (window, T, loud key, seen): the last query is at T - 1.
 EDGES = [(50, 300, 250, True), (50, 300, 249, False), (64, 640, 576, True), (64, 640, 575, False), (1, 130, 129, True), (1, 130, 128, False),
          (None, 700, 0, True), (None, 700, 15, True), (None, 700, 16, True), (500, 700, 200, True), (500, 700, 199, False),
-         (72, 200, 128, True), (72, 200, 127, False)]
+         (80, 200, 120, True), (80, 200, 119, False)]
 
 
 @pytest.mark.gpu
